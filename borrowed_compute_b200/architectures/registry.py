@@ -9,7 +9,7 @@ later architectures add rows to.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping
+from typing import Any, Callable, Dict, Mapping, Optional
 
 from ..config.errors import ConfigError
 from ..parts.base import ModelSpec
@@ -20,13 +20,16 @@ class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], Any]   # config.json dict -> typed configuration
     model_spec: Callable[[Any], ModelSpec]             # typed configuration -> layout of parts
+    # (config.json dict, tensor name -> shape) -> the dict with sizes filled in that the file leaves to the
+    # tensors' shapes; None for formats whose config.json says everything.
+    complete: Optional[Callable[[Mapping[str, Any], Mapping[str, tuple]], Dict[str, Any]]] = None
 
 
 _architectures: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config: Callable, model_spec: Callable) -> None:
-    _architectures[name] = Architecture(name, parse_config, model_spec)
+def register_architecture(name: str, parse_config: Callable, model_spec: Callable, complete: Optional[Callable] = None) -> None:
+    _architectures[name] = Architecture(name, parse_config, model_spec, complete)
 
 
 def unregister_architecture(name: str) -> None:
@@ -38,10 +41,13 @@ def architecture_names():
 
 
 def resolve(config: Mapping[str, Any]) -> Architecture:
-    """The architecture a config.json names."""
+    """The architecture a config.json names: the first of ``architectures`` (published
+    folders), or the one string of ``architecture``."""
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     if archs[0] not in _architectures:
         raise ConfigError(f"config.json: architecture {archs[0]!r} is not supported (known: {architecture_names()})")
     return _architectures[archs[0]]

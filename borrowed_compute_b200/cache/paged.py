@@ -8,14 +8,15 @@ the same window) form one *group* with storage of its own:
     table      [slots, pages a sequence can have] int32, -1 where no page is held
 
 A mixer that asks for state gets one tensor [slots, *shape] for its run, zeroed whenever a
-slot is handed out.  The reference's cache is one f32 buffer per layer and conversation
+slot is handed out; so does every other part of a block that asks for some (a short
+convolution's last inputs), under the name of its role in the block.  The reference's cache is one f32 buffer per layer and conversation
 (crates/bc-infer/src/gpu/mod.rs:294-342).
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -35,10 +36,12 @@ class _Group:
 class PagedCache:
     """Storage for every run of a model's schedule, sized by tokens, slots and the longest
     sequence.  ``needs[i]`` / ``states[i]`` are what run i's mixer asked for (or None);
-    ``memory_of[i]`` names the run whose memory run i reads instead of owning some."""
+    ``memory_of[i]`` names the run whose memory run i reads instead of owning some;
+    ``more_states[i]`` maps a role of run i's block to the state that part asked for."""
 
     def __init__(self, rt: Runtime, needs: Sequence[Optional[CacheNeed]], states: Sequence[Optional[StateNeed]],
-                 memory_of: Sequence[Optional[int]], max_tokens: int, n_slots: int, max_seq: int):
+                 memory_of: Sequence[Optional[int]], max_tokens: int, n_slots: int, max_seq: int,
+                 more_states: Optional[Sequence[Mapping[str, StateNeed]]] = None):
         self.rt = rt
         self.n_runs = len(needs)
         self.memory_of = list(memory_of)
@@ -55,7 +58,7 @@ class PagedCache:
             self.groups[g].runs.append(i)
         n_pages = max(1, pages_for(max_tokens))
         self.n_pages = n_pages
-        self.slots = SlotTable(n_slots, n_pages, max_seq, [GroupPlan(g.need.window) for g in self.groups])
+        self.slots = SlotTable(n_slots, n_pages, max_seq, [GroupPlan(g.need.window, g.need.chunk) for g in self.groups])
         for g in self.groups:
             g.planes = [torch.zeros((len(g.runs), n_pages, heads, PAGE, width), dtype=rt.dtype, device=rt.device)
                         for heads, width in g.need.planes]
@@ -66,14 +69,23 @@ class PagedCache:
         self.state: Dict[int, torch.Tensor] = {}
         for i, need in enumerate(states):
             if need is not None and self.memory_of[i] is None:
-                self.state[i] = torch.zeros((n_slots,) + tuple(need.shape), dtype=need.dtype, device=rt.device)
+                self.state[i] = torch.zeros((n_slots,) + tuple(need.shape), dtype=need.dtype or rt.dtype, device=rt.device)
+        self.more_state: Dict[int, Dict[str, torch.Tensor]] = {}
+        for i, named in enumerate(more_states or ()):
+            if named and self.memory_of[i] is None:
+                self.more_state[i] = {role: torch.zeros((n_slots,) + tuple(need.shape), dtype=need.dtype or rt.dtype, device=rt.device)
+                                      for role, need in named.items()}
 
     # -- slots
     def acquire(self) -> int:
         slot = self.slots.acquire()
-        for t in self.state.values():
+        for t in self.all_state():
             t[slot].zero_()
         return slot
+
+    def all_state(self) -> List[torch.Tensor]:
+        """Every per-sequence state tensor, the mixers' and the other parts'."""
+        return list(self.state.values()) + [t for named in self.more_state.values() for t in named.values()]
 
     def release(self, slot: int) -> None:
         self.slots.release(slot)
@@ -108,11 +120,13 @@ class PagedCache:
             mem.planes, mem.page_table = tuple(t[line] for t in grp.planes), grp.table
         if owner in self.state:
             mem.state = self.state[owner]
+        if owner in self.more_state:
+            mem.states = self.more_state[owner]
         return mem
 
     def bytes(self) -> int:
         total = sum(t.numel() * t.element_size() for g in self.groups for t in g.planes)
-        return total + sum(t.numel() * t.element_size() for t in self.state.values())
+        return total + sum(t.numel() * t.element_size() for t in self.all_state())
 
     def bytes_per_token(self) -> int:
         return sum(len(g.runs) * g.need.values_per_token() * g.planes[0].element_size() for g in self.groups)

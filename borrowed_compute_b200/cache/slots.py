@@ -60,10 +60,12 @@ class PagePool:
 
 @dataclass
 class GroupPlan:
-    """What one storage group keeps per sequence: every position (window 0) or the last
-    ``window`` of them."""
+    """What one storage group keeps per sequence: every position (window 0, chunk 0), the
+    last ``window`` of them, and/or only the chunk of ``chunk`` positions (counted from
+    position 0) that the oldest row of a step lies in, and what follows."""
 
     window: int = 0
+    chunk: int = 0
 
 
 @dataclass
@@ -129,10 +131,13 @@ class SlotTable:
     def _first_needed_page(self, g: int, new_len: int, rows: int) -> int:
         """The first page a step still reads when a sequence grows to ``new_len`` by
         ``rows`` new positions: the oldest new row looks back ``window`` positions."""
-        w = self.groups[g].window
-        if w <= 0:
-            return 0
-        oldest_seen = max(0, new_len - rows + 1 - w)
+        w, c = self.groups[g].window, self.groups[g].chunk
+        oldest_row = new_len - rows                  # position of the step's first new row
+        oldest_seen = 0
+        if w > 0:
+            oldest_seen = max(oldest_seen, oldest_row + 1 - w)
+        if c > 0:
+            oldest_seen = max(oldest_seen, max(0, oldest_row) // c * c)     # the first position of that row's chunk
         return oldest_seen // PAGE
 
     def reserve(self, slot: int, new_len: int, rows: int = 1) -> None:

@@ -1,4 +1,5 @@
 from .errors import CacheError, ConfigError, WeightsError
+from .fegidra import FegidraConfig
 from .llama import Llama3RopeScaling, LlamaConfig
 
-__all__ = ["CacheError", "ConfigError", "WeightsError", "Llama3RopeScaling", "LlamaConfig"]
+__all__ = ["CacheError", "ConfigError", "WeightsError", "FegidraConfig", "Llama3RopeScaling", "LlamaConfig"]

@@ -1,8 +1,11 @@
 // Causal grouped-query attention over the paged cache, one warp a (row, head).
 //
 // For the new row at position p of the sequence in `slot`, head h reads kv head
-// g = h / (H / G) and sees cached positions lo..p, lo = 0 or p + 1 - window:
-//   s_t = (q . k_t) / sqrt(D);  out = sum_t softmax(s)_t v_t
+// g = h / (H / G) and sees cached positions lo..p, where lo is 0, or p + 1 - window (a
+// sliding window), or the first position of p's chunk, floor(p / chunk) * chunk (chunks are
+// counted from the sequence's position 0), whichever is later:
+//   s_t = (q . k_t) * scale;  out = sum_t softmax(s)_t v_t
+// Keys have D values a head and values DV, which may differ.
 // (crates/bc-infer/src/model.rs:448-481).  Like the reference's kernel
 // (crates/bc-infer/src/gpu/kernels.h:271-324) it keeps a running maximum m, a running sum
 // l and a running weighted sum of values, rescaled by e^(m - m') when a tile of positions
@@ -12,7 +15,7 @@
 // the true 32-bit path for prompts and decoding alike, and stands as the checked twin of
 // the faster bf16 kernels.
 //
-// Cache layout of one layer: [page][kv_head][BC_PAGE][D]; page_table[slot][i] names the
+// Cache layout of one layer: keys [page][kv_head][BC_PAGE][D], values [page][kv_head][BC_PAGE][DV]; page_table[slot][i] names the
 // page of positions 64 i .. 64 i + 63.  Rows whose slot is negative are padding: their
 // output is zero.
 #include "common.cuh"
@@ -52,20 +55,20 @@ template <class T>
 __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
                                                                    const T* __restrict__ v_cache, const int* __restrict__ page_table,
                                                                    const int* __restrict__ row_pos, const int* __restrict__ row_slot,
-                                                                   T* __restrict__ out, int H, int G, int D, int max_pages, int n_pages,
-                                                                   int window, float scale) {
+                                                                   T* __restrict__ out, int H, int G, int D, int DV, int max_pages,
+                                                                   int n_pages, int window, int chunk, float scale) {
     __shared__ __align__(16) float qs[WARPS][MAX_D];
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = blockIdx.x, h = blockIdx.y * WARPS + warp;
     if (h >= H) return;
-    T* o = out + ((size_t)r * H + h) * D;
+    T* o = out + ((size_t)r * H + h) * DV;
     const int slot = row_slot[r];
-    const int nd = (D + 31) / 32;
+    const int nd = (DV + 31) / 32;
     if (slot < 0) {
         for (int j = 0; j < nd; j++)
-            if (lane + 32 * j < D) o[lane + 32 * j] = from_f32<T>(0.0f);
+            if (lane + 32 * j < DV) o[lane + 32 * j] = from_f32<T>(0.0f);
         return;
     }
     const int pos = row_pos[r];
@@ -74,7 +77,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
     for (int d = lane; d < D; d += 32) qs[warp][d] = to_f32(qh[d]);
     __syncwarp();
 
-    const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+    int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
     const int* pages = page_table + (size_t)slot * max_pages;
     float acc[MAX_D / 32];
 #pragma unroll
@@ -85,7 +89,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
         const int pi = t0 / BC_PAGE;
         int page = pi < max_pages ? pages[pi] : -1;
         if (page < 0 || page >= n_pages) page = -1;
-        const size_t base = (((size_t)(page < 0 ? 0 : page) * G + g) * BC_PAGE + (t0 % BC_PAGE)) * D;
+        const size_t at = ((size_t)(page < 0 ? 0 : page) * G + g) * BC_PAGE + (t0 % BC_PAGE);
+        const size_t base = at * D;
         const int t = t0 + lane;
         const bool seen = page >= 0 && t >= lo && t <= pos;
         float s = -INFINITY;
@@ -97,13 +102,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
 #pragma unroll
         for (int j = 0; j < MAX_D / 32; j++) acc[j] *= corr;
         const int count = page < 0 ? 0 : min(32, pos + 1 - t0);
-        const T* vt = v_cache + base;
-        for (int i = 0; i < count; i++) {
+        const T* vt = v_cache + at * DV;
+        for (int i = max(0, lo - t0); i < count; i++) {
             const float pi_ = __shfl_sync(0xffffffffu, p, i);
 #pragma unroll
             for (int j = 0; j < MAX_D / 32; j++) {
                 const int d = lane + 32 * j;
-                if (j < nd && d < D) acc[j] = fmaf(pi_, to_f32(vt[(size_t)i * D + d]), acc[j]);
+                if (j < nd && d < DV) acc[j] = fmaf(pi_, to_f32(vt[(size_t)i * DV + d]), acc[j]);
             }
         }
         m = mn;
@@ -112,21 +117,22 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
 #pragma unroll
     for (int j = 0; j < MAX_D / 32; j++) {
         const int d = lane + 32 * j;
-        if (j < nd && d < D) o[d] = from_f32<T>(acc[j] * inv);
+        if (j < nd && d < DV) o[d] = from_f32<T>(acc[j] * inv);
     }
 }
 
 template <class T>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
-                  const int* row_slot, void* out, int rows, int H, int G, int D, int max_pages, int n_pages, int window, float scale,
-                  cudaStream_t s) {
+                  const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk,
+                  float scale, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && H > 0 && G > 0 && H % G == 0, "attention_rows: bad sizes rows=%d H=%d G=%d", rows, H, G);
-    BC_CHECK_ARG(D > 0 && D % 16 == 0 && D <= MAX_D, "attention_rows: head size %d is not a multiple of 16 up to %d", D, MAX_D);
+    BC_CHECK_ARG(D > 0 && D % 8 == 0 && D <= MAX_D, "attention_rows: head size %d is not a multiple of 8 up to %d", D, MAX_D);
+    BC_CHECK_ARG(DV > 0 && DV <= MAX_D && window >= 0 && chunk >= 0, "attention_rows: bad value width %d, window %d or chunk %d", DV, window, chunk);
     BC_CHECK_ARG(rows <= 2147483647 && (H + WARPS - 1) / WARPS <= 65535, "attention_rows: too many heads (%d)", H);
     if (rows == 0) return BC_OK;
     dim3 grid(rows, (H + WARPS - 1) / WARPS);
     bc_launch(attention_rows_kernel<T>, grid, dim3(WARPS * 32), 0, s, (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, page_table,
-              row_pos, row_slot, (T*)out, H, G, D, max_pages, n_pages, window, scale);
+              row_pos, row_slot, (T*)out, H, G, D, DV, max_pages, n_pages, window, chunk, scale);
     BC_LAUNCH_STATUS();
 }
 
@@ -134,10 +140,22 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
 extern "C" int bc_attention_rows_f32(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                      const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int max_pages,
                                      int n_pages, int window, float scale, cudaStream_t s) {
-    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, max_pages, n_pages, window, scale, s);
+    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, s);
 }
 extern "C" int bc_attention_rows_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                       const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int max_pages,
                                       int n_pages, int window, float scale, cudaStream_t s) {
-    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, max_pages, n_pages, window, scale, s);
+    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, s);
+}
+
+// The same with values of their own width DV (out: [rows, H, DV]) and a chunk mask beside the window (0: none).
+extern "C" int bc_attention_rows_kv_f32(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                        const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
+                                        int n_pages, int window, int chunk, float scale, cudaStream_t s) {
+    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, s);
+}
+extern "C" int bc_attention_rows_kv_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                         const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
+                                         int n_pages, int window, int chunk, float scale, cudaStream_t s) {
+    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, s);
 }

@@ -1,0 +1,107 @@
+// What lies between the fused q/k/v product and attention when queries and keys are
+// normalised as wholes: for every row
+//   q, k, v  += their biases (if any)
+//   q, k      = RMS norm over the whole projection (all heads at once), times a weight
+//   q, k      rotated by the row's position on the first `rot` dimensions of each head,
+//             dimension i paired with i + rot/2 (the rest pass unchanged)
+//   q        -> the activation type, for the attention kernel
+//   k, v     -> the row's place in the paged cache (planes of different widths D and DV)
+// The projection arrives as float (the product's accumulators); statistics, angles and the
+// rotation are float.  One block a row.
+#include "common.cuh"
+
+template <class T>
+__global__ void __launch_bounds__(256)
+qkv_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ q_weight,
+                   const float* __restrict__ k_weight, const float* __restrict__ cos_sin, int n_positions, const int* __restrict__ row_pos,
+                   const int* __restrict__ row_slot, const int* __restrict__ page_table, int max_pages, int n_pages, T* __restrict__ q_out,
+                   T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int D, int DV, int rot, float eps, int normed,
+                   int write_cache) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int nq = H * D, nk = G * D, nv = G * DV;
+    const float* x = qkv + (size_t)r * (nq + nk + nv);
+    const int slot = row_slot[r];
+    const int pos = row_pos[r];
+    float q_scale = 1.0f, k_scale = 1.0f;
+    if (normed) {
+        float sq = 0.0f, sk = 0.0f;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+            const float v = x[i] + (bias ? bias[i] : 0.0f);
+            sq = fmaf(v, v, sq);
+        }
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+            const float v = x[nq + i] + (bias ? bias[nq + i] : 0.0f);
+            sk = fmaf(v, v, sk);
+        }
+        q_scale = 1.0f / sqrtf(block_sum(sq, scratch) / (float)nq + eps);
+        k_scale = 1.0f / sqrtf(block_sum(sk, scratch) / (float)nk + eps);
+    }
+    const int half = rot / 2;
+    const bool turn = rot > 0 && cos_sin != nullptr && pos >= 0 && pos < n_positions;
+    const float* cs = cos_sin + (size_t)(turn ? pos : 0) * half * 2;
+    int page = -1;
+    if (slot >= 0 && pos >= 0 && pos / BC_PAGE < max_pages) page = page_table[(size_t)slot * max_pages + pos / BC_PAGE];
+    if (page >= n_pages) page = -1;
+    // Queries and keys are one loop: element i < nq is a query, the others keys.
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        const bool is_q = i < nq;
+        const int e = is_q ? i : i - nq;
+        const int d = e % D;
+        const float scale = is_q ? q_scale : k_scale;
+        const float* wt = is_q ? q_weight : k_weight;
+        float v = (x[i] + (bias ? bias[i] : 0.0f)) * scale * (normed ? wt[e] : 1.0f);
+        if (turn && d < rot) {
+            const int other = d < half ? i + half : i - half, eo = d < half ? e + half : e - half;
+            const float p = (x[other] + (bias ? bias[other] : 0.0f)) * scale * (normed ? wt[eo] : 1.0f);
+            const float c = cs[2 * (d % half)], s = cs[2 * (d % half) + 1];
+            v = d < half ? v * c - p * s : v * c + p * s;
+        }
+        if (is_q) {
+            q_out[(size_t)r * nq + e] = from_f32<T>(v);
+        } else if (write_cache && page >= 0) {
+            const int g = e / D;
+            k_cache[(((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * D + d] = from_f32<T>(v);
+        }
+    }
+    if (write_cache && page >= 0) {
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            const int g = i / DV, d = i % DV;
+            v_cache[(((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * DV + d] = from_f32<T>(x[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.0f));
+        }
+    }
+}
+
+template <class T>
+static int launch(const float* qkv, const float* bias, const float* q_weight, const float* k_weight, const float* cos_sin, int n_positions,
+                  const int* row_pos, const int* row_slot, const int* page_table, int max_pages, int n_pages, void* q_out, void* k_cache,
+                  void* v_cache, int rows, int H, int G, int D, int DV, int rot, float eps, int normed, int write_cache, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && H > 0 && G > 0 && D > 0 && DV > 0, "qkv_prepare: bad sizes rows=%d H=%d G=%d D=%d DV=%d", rows, H, G, D, DV);
+    BC_CHECK_ARG(rot >= 0 && rot % 2 == 0 && rot <= D, "qkv_prepare: %d rotated dimensions of a head of %d", rot, D);
+    BC_CHECK_ARG(!normed || (q_weight && k_weight), "qkv_prepare: the norm needs its weights");
+    if (rows == 0) return BC_OK;
+    bc_launch(qkv_prepare_kernel<T>, dim3(rows), dim3(256), 0, s, qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot,
+              page_table, max_pages, n_pages, (T*)q_out, (T*)k_cache, (T*)v_cache, H, G, D, DV, rot, eps, normed, write_cache);
+    BC_LAUNCH_STATUS();
+}
+
+// qkv: [rows, H D + G D + G DV] float; bias: the same width or null; q_weight [H D], k_weight [G D]
+// (used when normed); cos_sin: [n_positions, rot / 2, 2] or null; q_out: [rows, H D];
+// k_cache [pages, G, PAGE, D], v_cache [pages, G, PAGE, DV].  Rows whose slot is negative
+// write no cache.
+extern "C" int bc_qkv_prepare_f32(const float* qkv, const float* bias, const float* q_weight, const float* k_weight, const float* cos_sin,
+                                  int n_positions, const int* row_pos, const int* row_slot, const int* page_table, int max_pages, int n_pages,
+                                  void* q_out, void* k_cache, void* v_cache, int rows, int H, int G, int D, int DV, int rot, float eps,
+                                  int normed, int write_cache, cudaStream_t s) {
+    return launch<float>(qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot, page_table, max_pages, n_pages, q_out, k_cache,
+                         v_cache, rows, H, G, D, DV, rot, eps, normed, write_cache, s);
+}
+extern "C" int bc_qkv_prepare_bf16(const float* qkv, const float* bias, const float* q_weight, const float* k_weight, const float* cos_sin,
+                                   int n_positions, const int* row_pos, const int* row_slot, const int* page_table, int max_pages, int n_pages,
+                                   void* q_out, void* k_cache, void* v_cache, int rows, int H, int G, int D, int DV, int rot, float eps,
+                                   int normed, int write_cache, cudaStream_t s) {
+    return launch<bf16>(qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot, page_table, max_pages, n_pages, q_out, k_cache,
+                        v_cache, rows, H, G, D, DV, rot, eps, normed, write_cache, s);
+}

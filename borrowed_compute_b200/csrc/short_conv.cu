@@ -1,0 +1,103 @@
+// A short causal convolution over time on every channel, added to its own input:
+//   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - (taps - 1 - j), c]
+// with zeros before a sequence's first position.  The last taps - 1 inputs of a sequence
+// are state that outlives the step: tail[slot][i][c] holds the input at position
+// start - (taps - 1) + i, where `start` is how many positions the slot held before this
+// step (a slot handed out anew holds zeros there, which is the convolution's padding).
+//
+// Every (row, channel) is one thread's sum of `taps` terms in ascending j, so a row's result
+// is the same bits whether it came in a prompt, in a portion of one, or alone.  The products
+// and the sum are float; inputs, outputs and the tail have the activation type.
+//
+// Two launches a prompt step: the convolution (which only reads the tail) and then the new
+// tail.  A step of one row a sequence does both in one launch: a channel of a sequence is
+// then one thread's alone.
+#include "common.cuh"
+
+#define SC_THREADS 256
+
+template <class T>
+__global__ void __launch_bounds__(SC_THREADS)
+short_conv_kernel(const T* __restrict__ h, const float* __restrict__ w, T* __restrict__ tail, const int* __restrict__ seq_rows,
+                  const int* __restrict__ seq_slot, T* __restrict__ out, int E, int taps, int n_slots, int update_tail) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tok = blockIdx.x, sq = blockIdx.y;
+    const int c = blockIdx.z * SC_THREADS + threadIdx.x;
+    const int slot = seq_slot[sq];
+    const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
+    if (slot < 0 || slot >= n_slots || tok >= n_new || c >= E) return;
+    T* tl = tail + (size_t)slot * (taps - 1) * E + c;
+    const T* hr = h + (size_t)row0 * E + c;
+    const float own = to_f32(hr[(size_t)tok * E]);
+    float acc = 0.0f;
+    for (int j = 0; j < taps; j++) {
+        const int back = taps - 1 - j;
+        // The input `back` positions earlier: a row of this step, or one the tail kept.
+        const float v = back == 0 ? own : back <= tok ? to_f32(hr[(size_t)(tok - back) * E]) : to_f32(tl[(size_t)(tok - back + taps - 1) * E]);
+        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    }
+    out[(size_t)(row0 + tok) * E + c] = from_f32<T>(own + acc);
+    if (update_tail) {
+        // One row a sequence: the tail moves up by one and takes this row's input.
+        for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
+        if (taps > 1) tl[(size_t)(taps - 2) * E] = from_f32<T>(own);
+    }
+}
+
+// The tail after the step: the inputs at the last taps - 1 positions the sequence now holds,
+// from this step's rows where they reach that far back, else from the old tail (entry i takes
+// old entry i + n_new, which lies above it, so ascending i never reads what it has written).
+template <class T>
+__global__ void __launch_bounds__(SC_THREADS)
+short_conv_tail_kernel(const T* __restrict__ h, T* __restrict__ tail, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot,
+                       int E, int taps, int n_slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int sq = blockIdx.x;
+    const int c = blockIdx.y * SC_THREADS + threadIdx.x;
+    const int slot = seq_slot[sq];
+    const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
+    if (slot < 0 || slot >= n_slots || n_new <= 0 || c >= E) return;
+    T* tl = tail + (size_t)slot * (taps - 1) * E + c;
+    for (int i = 0; i < taps - 1; i++) {
+        const int rel = n_new - (taps - 1) + i;      // which row of this step, if not negative
+        tl[(size_t)i * E] = rel >= 0 ? h[(size_t)(row0 + rel) * E + c] : tl[(size_t)(i + n_new) * E];
+    }
+}
+
+template <class T>
+static int launch(const void* h, const float* w, void* tail, const int* seq_rows, const int* seq_slot, void* out, int seqs, int max_new,
+                  int E, int taps, int n_slots, int write_tail, cudaStream_t s) {
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && E > 0 && taps >= 1, "short_conv: bad sizes seqs=%d max_new=%d E=%d taps=%d",
+                 seqs, max_new, E, taps);
+    BC_CHECK_ARG((E + SC_THREADS - 1) / SC_THREADS <= 65535, "short_conv: %d channels are too many", E);
+    if (seqs == 0 || max_new == 0) return BC_OK;
+    const int chunks = (E + SC_THREADS - 1) / SC_THREADS;
+    const int fused = write_tail && max_new == 1;
+    bc_launch(short_conv_kernel<T>, dim3(max_new, seqs, chunks), dim3(SC_THREADS), 0, s, (const T*)h, w, (T*)tail, seq_rows, seq_slot, (T*)out,
+              E, taps, n_slots, fused);
+    if (write_tail && !fused && taps > 1) {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            bc_set_error("short_conv: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        bc_launch(short_conv_tail_kernel<T>, dim3(seqs, chunks), dim3(SC_THREADS), 0, s, (const T*)h, (T*)tail, seq_rows, seq_slot, E, taps,
+                  n_slots);
+    }
+    BC_LAUNCH_STATUS();
+}
+
+// h, out: [rows, E]; w: [E, taps] float; tail: [n_slots, taps - 1, E].  Sequence s owns rows
+// seq_rows[s] .. seq_rows[s + 1] and lives in slot seq_slot[s] (negative: skipped, its rows of
+// `out` are left untouched).  max_new: the most rows any sequence brings.  write_tail 0 leaves
+// the tail as it was (a run that reads another run's memory).
+extern "C" int bc_short_conv_f32(const void* h, const float* w, void* tail, const int* seq_rows, const int* seq_slot, void* out, int seqs,
+                                 int max_new, int E, int taps, int n_slots, int write_tail, cudaStream_t s) {
+    return launch<float>(h, w, tail, seq_rows, seq_slot, out, seqs, max_new, E, taps, n_slots, write_tail, s);
+}
+extern "C" int bc_short_conv_bf16(const void* h, const float* w, void* tail, const int* seq_rows, const int* seq_slot, void* out, int seqs,
+                                  int max_new, int E, int taps, int n_slots, int write_tail, cudaStream_t s) {
+    return launch<bf16>(h, w, tail, seq_rows, seq_slot, out, seqs, max_new, E, taps, n_slots, write_tail, s);
+}

@@ -159,7 +159,8 @@ class Engine:
         self.max_seq = max_seq
         self.stop_ids: tuple = tuple(model.spec.stop_ids)    # ids that end a sequence by default: config.json's, plus generation_config.json's
         needs, states, memory_of = model.memory_needs()
-        self.cache = PagedCache(rt, needs, states, memory_of, max_tokens=max_tokens, n_slots=max_slots, max_seq=max_seq)
+        self.cache = PagedCache(rt, needs, states, memory_of, max_tokens=max_tokens, n_slots=max_slots, max_seq=max_seq,
+                                more_states=model.more_state_needs())
         self._ints: Optional[torch.Tensor] = None
         self._host_ints: Optional[torch.Tensor] = None
         self._staged: Optional[torch.cuda.Event] = None
@@ -206,10 +207,11 @@ class Engine:
         total)`` is called after every tensor brought to the device (the reference reports
         bytes fetched as it goes, crates/bc-infer/src/lib.rs:33-47)."""
         config = read_config_json(folder)
-        typed, model = model_for_config(config)
+        source = TensorSource(folder)
+        typed, model = model_for_config(config, {n: tuple(source.info(n)[1]) for n in source.names()})
         rt = cls._runtime(dtype, device)
         eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
-        model.load(load_tensors(model.expected_tensors(), TensorSource(folder), rt, progress), rt)
+        model.load(load_tensors(model.expected_tensors(), source, rt, progress), rt)
         more = read_generation_stop_ids(folder, eng.vocab_size)
         eng.stop_ids = tuple(dict.fromkeys(eng.stop_ids + more))
         return eng
@@ -243,7 +245,7 @@ class Engine:
         """Tensors given by name in memory, checked like a folder's."""
         from ..weights.loader import check_tensors, device_type
 
-        typed, model = model_for_config(config)
+        typed, model = model_for_config(config, {n: tuple(t.shape) for n, t in tensors.items()})
         rt = cls._runtime(dtype, device)
         eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
         expected = model.expected_tensors()
@@ -280,17 +282,26 @@ class Engine:
         if length == have:
             return
         self.cache.slots.check_rollback(slot, length)
-        saved = {run: state[slot].clone() for run, state in self.cache.state.items()}
-        for run, state in self.cache.state.items():
-            if length == 0:
+        every = self.cache.all_state()
+        saved = [state[slot].clone() for state in every]
+
+        def refuse(run: int, who: str):
+            for state, old in zip(every, saved):
+                state[slot].copy_(old)
+            raise CacheError(f"slot {slot} cannot go back to {length} positions: the {who} of run {run} keeps per-sequence "
+                             f"state and cannot restore it (only a cut to 0 is always possible)")
+
+        if length == 0:
+            for state in every:
                 state[slot].zero_()
-                continue
-            mixer = self.model.blocks[self.model.spec.schedule[run].layer].memory_part()
-            if not mixer.rollback_state(state, slot, length):
-                for r, old in saved.items():
-                    self.cache.state[r][slot].copy_(old)
-                raise CacheError(f"slot {slot} cannot go back to {length} positions: the mixer of run {run} keeps per-sequence "
-                                 f"state and cannot restore it (only a cut to 0 is always possible)")
+        else:
+            for run, state in self.cache.state.items():
+                mixer = self.model.blocks[self.model.spec.schedule[run].layer].memory_part()
+                if not mixer.rollback_state(state, slot, length):
+                    refuse(run, "mixer")
+            for run, named in self.cache.more_state.items():
+                if not self.model.blocks[self.model.spec.schedule[run].layer].rollback_states(named, slot, length):
+                    refuse(run, "block")
         self.cache.slots.rollback(slot, length)
 
     # -------------------------------------------------------------------------------- step

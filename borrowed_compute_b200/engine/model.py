@@ -65,6 +65,10 @@ class DecoderModel:
             memory_of.append(run.memory_of)
         return needs, states, memory_of
 
+    def more_state_needs(self) -> List[Dict[str, StateNeed]]:
+        """For every run, the per-sequence state its block's other parts ask for, by role."""
+        return [dict(self.blocks[run.layer].state_needs()) for run in self.spec.schedule]
+
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor], n_want: int) -> torch.Tensor:
         """Scores [n_want, vocab] float32 at rows ``want_rows`` (all rows if None)."""
         rt = self.rt
@@ -81,9 +85,13 @@ class DecoderModel:
         return scores
 
 
-def model_for_config(config: Mapping[str, Any]) -> Tuple[Any, DecoderModel]:
-    """The typed configuration and the (unloaded) model a config.json dict describes."""
+def model_for_config(config: Mapping[str, Any], shapes: Optional[Mapping[str, tuple]] = None) -> Tuple[Any, DecoderModel]:
+    """The typed configuration and the (unloaded) model a config.json dict describes.
+    ``shapes`` (tensor name -> shape of what the folder holds) lets an architecture whose
+    config.json leaves a size to the tensors fill it in."""
     arch = resolve(config)
+    if arch.complete is not None and shapes is not None:
+        config = arch.complete(config, shapes)
     typed = arch.parse_config(config)
     return typed, DecoderModel(arch.model_spec(typed))
 

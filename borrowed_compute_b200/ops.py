@@ -143,6 +143,7 @@ label = ""
 _CLASS_OF = {
     "bc_embed": "embedding", "bc_rmsnorm": "norm", "bc_swiglu": "activation", "bc_rope_append": "rotary + append",
     "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
+    "bc_short_conv": "short convolution", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
 }
 
@@ -512,8 +513,10 @@ def attention_prefill_tc_status(reset: bool = True) -> int:
 
 def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                    row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
-                   window: int = 0, scale: Optional[float] = None) -> None:
-    """Causal attention of every row against its slot's cached positions, one warp a (row, head)."""
+                   window: int = 0, scale: Optional[float] = None, value_dim: Optional[int] = None, chunk: int = 0) -> None:
+    """Causal attention of every row against its slot's cached positions, one warp a (row, head).
+    ``value_dim`` (default: ``head_dim``) is the width of a head's values, ``chunk`` > 0 lets a
+    position see only those of its own chunk of that many positions, counted from position 0."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
@@ -522,16 +525,145 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
     _need(row_slot, "row_slot", torch.int32)
     _need(out, "out", q.dtype)
     rows = out.shape[0]
-    if out.shape[1] != heads * head_dim:
-        raise KernelError(f"attention: out width {out.shape[1]} is not heads * head_dim")
-    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
-        raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    if out.shape[1] != heads * value_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * value_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], kv_heads, PAGE, value_dim):
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)} and {tuple(v_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, "
+                          f"{head_dim}] and [pages, {kv_heads}, {PAGE}, {value_dim}]")
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
     _bounds_paged("attention_rows", rows, row_pos, row_slot, page_table, k_cache.shape[0])
-    _call(_fn("bc_attention_rows_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
-          _ptr(row_pos), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
+    _call(_fn("bc_attention_rows_kv_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+          _ptr(row_pos), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim),
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+
+
+# ------------------------------------------------------- parts of other mixers and feed-forwards
+
+def short_conv(h: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
+               out: torch.Tensor, seqs: int, max_new: int, write_tail: bool = True) -> None:
+    """out = h + causal convolution of h over time on every channel; ``weight`` [E, taps] float32,
+    ``tail`` [slots, taps - 1, E] holds every slot's last inputs and is brought up to date."""
+    _need(h, "h")
+    _need(weight, "weight", torch.float32)
+    _need(tail, "tail", h.dtype)
+    _need(seq_rows, "seq_rows", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    _need(out, "out", h.dtype)
+    E, taps = weight.shape
+    if h.shape[-1] != E or out.shape != h.shape or tuple(tail.shape[1:]) != (taps - 1, E):
+        raise KernelError(f"short_conv: h {tuple(h.shape)}, out {tuple(out.shape)}, tail {tuple(tail.shape)} do not fit weight {(E, taps)}")
+    if h.data_ptr() == out.data_ptr():
+        raise KernelError("short_conv: out must not be h (rows read their predecessors)")
+    _bounds("short_conv: seq_slot", seq_slot, tail.shape[0], seqs, lowest=-1)
+    _bounds("short_conv: seq_rows", seq_rows, h.shape[0] + 1, seqs + 1)
+    _call(_fn("bc_short_conv_" + _suffix(h.dtype)), _ptr(h), _ptr(weight), _ptr(tail), _ptr(seq_rows), _ptr(seq_slot), _ptr(out),
+          _c_int(seqs), _c_int(max_new), _c_int(E), _c_int(taps), _c_int(tail.shape[0]), _c_int(1 if write_tail else 0), _stream())
+
+
+def delta_prepare(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, decay: torch.Tensor, unit: torch.Tensor,
+                  removal: torch.Tensor, dots: torch.Tensor, heads: int, head_dim: int, decay_scale: float, key_eps: float) -> None:
+    """From the fused projection [rows, 5 H D + inner] (r, k, v, gate, a, decay's inner projection; float32): per key
+    channel the decay exp(-decay_scale * sigmoid(w2 tanh(inner) + w0)), the key over its length, the removal
+    rate sigmoid(a + a_bias) times that unit key, and per head the dot products r.(removal) and r.k."""
+    rows, stride = proj.shape
+    HD = heads * head_dim
+    inner = w2.shape[1]
+    for t, name in ((proj, "proj"), (w2, "w2"), (w0, "w0"), (a_bias, "a_bias"), (decay, "decay"), (unit, "unit"), (removal, "removal"), (dots, "dots")):
+        _need(t, name, torch.float32)
+    if w2.shape[0] != HD or w0.numel() != HD or a_bias.numel() != HD or stride != 5 * HD + inner:
+        raise KernelError(f"delta_prepare: proj {tuple(proj.shape)}, w2 {tuple(w2.shape)} do not fit {heads} heads of {head_dim}")
+    if any(tuple(t.shape) != (rows, HD) for t in (decay, unit, removal)) or tuple(dots.shape) != (rows, heads, 2):
+        raise KernelError("delta_prepare: outputs must be [rows, H D] and dots [rows, H, 2]")
+    _call(_fn("bc_delta_prepare"), _ptr(proj), _c_int(stride), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(decay), _ptr(unit), _ptr(removal),
+          _ptr(dots), _c_int(rows), _c_int(heads), _c_int(head_dim), _c_int(inner), _c_float(decay_scale), _c_float(key_eps), _stream())
+
+
+def delta_scan(proj: torch.Tensor, decay: torch.Tensor, unit: torch.Tensor, removal: torch.Tensor, dots: torch.Tensor, state: torch.Tensor,
+               seq_rows: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, seqs: int, heads: int, head_dim: int,
+               write_state: bool = True) -> None:
+    """The recurrence S <- diag(decay) S - removal (unit^T S) + k v^T, o = S^T r over every sequence's rows in
+    time order, from and into ``state`` [slots, H, D, D] float32; ``out`` [rows, H D] float32."""
+    for t, name in ((proj, "proj"), (decay, "decay"), (unit, "unit"), (removal, "removal"), (dots, "dots"), (state, "state"), (out, "out")):
+        _need(t, name, torch.float32)
+    _need(seq_rows, "seq_rows", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    if tuple(state.shape[1:]) != (heads, head_dim, head_dim) or out.shape != decay.shape or proj.shape[1] < 3 * heads * head_dim:
+        raise KernelError(f"delta_scan: state {tuple(state.shape)} or out {tuple(out.shape)} do not fit {heads} heads of {head_dim}")
+    _bounds("delta_scan: seq_slot", seq_slot, state.shape[0], seqs, lowest=-1)
+    _bounds("delta_scan: seq_rows", seq_rows, proj.shape[0] + 1, seqs + 1)
+    _call(_fn("bc_delta_scan"), _ptr(proj), _c_int(proj.shape[1]), _ptr(decay), _ptr(unit), _ptr(removal), _ptr(dots), _ptr(state),
+          _ptr(seq_rows), _ptr(seq_slot), _ptr(out), _c_int(seqs), _c_int(heads), _c_int(head_dim), _c_int(state.shape[0]),
+          _c_int(1 if write_state else 0), _stream())
+
+
+def delta_finish(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor, heads: int, head_dim: int,
+                 eps: float) -> None:
+    """out = o / rms(o over each head) * weight * sigmoid(gate), the gate at columns gate_offset .. of ``proj``."""
+    _need(o, "o", torch.float32)
+    _need(proj, "proj", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    rows, HD = o.shape
+    if HD != heads * head_dim or out.shape != o.shape or weight.numel() != HD or gate_offset + HD > proj.shape[1] or proj.shape[0] != rows:
+        raise KernelError("delta_finish: shapes do not fit")
+    gate = proj.reshape(-1)[gate_offset:]
+    _call(_fn("bc_delta_finish_" + _suffix(out.dtype)), _ptr(o), _c_void_p(gate.data_ptr()), _c_int(proj.shape[1]), _ptr(weight), _ptr(out),
+          _c_int(rows), _c_int(heads), _c_int(head_dim), _c_float(eps), _stream())
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e with (a, b, c, e) = coef and N the division of a row by its root mean square."""
+    _need(z, "z", torch.float32)
+    _need(coef, "coef", torch.float32)
+    _need(out, "out")
+    if coef.numel() != 4 or out.shape != z.shape:
+        raise KernelError(f"polynorm: coef has {coef.numel()} numbers (wanted 4) or out {tuple(out.shape)} is not z {tuple(z.shape)}")
+    _call(_fn("bc_polynorm_" + _suffix(out.dtype)), _ptr(z), _ptr(coef), _ptr(out), _c_int(z.shape[0]), _c_int(z.shape[1]), _c_float(eps),
+          _stream())
+
+
+def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_slot: torch.Tensor, page_table: torch.Tensor,
+                q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                value_dim: int, rot_dims: int, eps: float, write_cache: bool = True) -> None:
+    """Between the fused projection (float32) and attention: biases, RMS norm of q and of k over all heads at once
+    (when weights are given), rotation of the first ``rot_dims`` dimensions of each head (i paired with i + rot_dims/2),
+    q into ``q_out`` and k, v into the rows' places in the paged cache."""
+    _need(qkv, "qkv", torch.float32)
+    _need(q_out, "q_out")
+    _need(k_cache, "k_cache", q_out.dtype)
+    _need(v_cache, "v_cache", q_out.dtype)
+    _need(row_pos, "row_pos", torch.int32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(page_table, "page_table", torch.int32)
+    rows = qkv.shape[0]
+    nq, nk, nv = heads * head_dim, kv_heads * head_dim, kv_heads * value_dim
+    if qkv.shape[1] != nq + nk + nv or tuple(q_out.shape) != (rows, nq):
+        raise KernelError(f"qkv_prepare: qkv {tuple(qkv.shape)} or q_out {tuple(q_out.shape)} do not fit the head sizes")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], kv_heads, PAGE, value_dim):
+        raise KernelError(f"qkv_prepare: cache is {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    for t, name, n in ((bias, "bias", nq + nk + nv), (q_weight, "q_weight", nq), (k_weight, "k_weight", nk)):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"qkv_prepare: {name} has {t.numel()} values, wanted {n}")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qkv_prepare: the norm needs both weights or none")
+    n_positions = 0
+    if cos_sin is not None and rot_dims > 0:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape[1] != rot_dims // 2:
+            raise KernelError(f"qkv_prepare: the rotary table has {cos_sin.shape[1]} pairs, {rot_dims} rotated dimensions want {rot_dims // 2}")
+        n_positions = cos_sin.shape[0]
+        _bounds("qkv_prepare: row_pos", row_pos, n_positions, rows)
+    _bounds_paged("qkv_prepare", rows, row_pos, row_slot, page_table, k_cache.shape[0])
+    _call(_fn("bc_qkv_prepare_" + _suffix(q_out.dtype)), _ptr(qkv), _ptr(bias), _ptr(q_weight), _ptr(k_weight),
+          _ptr(cos_sin if n_positions else None), _c_int(n_positions), _ptr(row_pos), _ptr(row_slot), _ptr(page_table),
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(rows), _c_int(heads),
+          _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(rot_dims if n_positions else 0), _c_float(eps),
+          _c_int(0 if q_weight is None else 1), _c_int(1 if write_cache else 0), _stream())
 
 
 _decode_scratch = {}

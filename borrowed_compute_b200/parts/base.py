@@ -7,6 +7,8 @@ A model is put together from parts that know nothing of the model they are in:
   the cache gives it: token-indexed pages, or per-sequence state of fixed size;
 - a *feed-forward* maps rows to rows;
 - a *position encoding* is a parameter of a mixer (rotary tables) or acts on embeddings;
+- a *short convolution* mixes a few neighbouring rows of one sequence on every channel and
+  keeps the last of them as per-sequence state;
 - a *block* arranges norms, a mixer and a feed-forward around the residual stream.
 
 Each kind has a registry from a name to a class.  A model's specification
@@ -59,6 +61,7 @@ NORMS = Registry("norm")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 POSITION_ENCODINGS = Registry("position encoding")
+CONVOLUTIONS = Registry("short convolution")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
@@ -162,10 +165,13 @@ class CacheNeed:
     page of 64 positions at a time as [pages, heads, 64, width].  Attention asks for two
     equal planes (keys, values); a mixer that caches one latent vector a token asks for
     one plane (1, width); planes may differ in shape.  ``window`` > 0 if only that many
-    latest positions are ever read.  Runs with equal needs share one storage group."""
+    latest positions are ever read; ``chunk`` > 0 if a position only ever reads those of its
+    own chunk of that many positions (counted from position 0), so that whole chunks behind
+    the newest one can be let go.  Runs with equal needs share one storage group."""
 
     planes: Tuple[Tuple[int, int], ...]
     window: int = 0
+    chunk: int = 0
 
     def __post_init__(self):
         self.planes = tuple((int(h), int(w)) for h, w in self.planes)
@@ -173,12 +179,13 @@ class CacheNeed:
             raise ValueError(f"a cache need wants at least one plane of positive sizes, got {self.planes}")
 
     @staticmethod
-    def keys_values(kv_heads: int, head_dim: int, window: int = 0) -> "CacheNeed":
-        """Keys and values of ``kv_heads`` heads of ``head_dim`` a position."""
-        return CacheNeed(((kv_heads, head_dim), (kv_heads, head_dim)), window)
+    def keys_values(kv_heads: int, head_dim: int, window: int = 0, value_dim: Optional[int] = None, chunk: int = 0) -> "CacheNeed":
+        """Keys of ``kv_heads`` heads of ``head_dim`` a position, and values of ``value_dim``
+        (default: the same width)."""
+        return CacheNeed(((kv_heads, head_dim), (kv_heads, head_dim if value_dim is None else value_dim)), window, chunk)
 
     def key(self) -> Tuple:
-        return (self.planes, self.window)
+        return (self.planes, self.window, self.chunk)
 
     def values_per_token(self) -> int:
         return sum(h * w for h, w in self.planes)
@@ -187,10 +194,11 @@ class CacheNeed:
 @dataclass
 class StateNeed:
     """Per-sequence memory of fixed size a mixer wants: one tensor of ``shape`` and
-    ``dtype`` per slot, zeroed when the slot is handed out."""
+    ``dtype`` per slot, zeroed when the slot is handed out.  ``dtype`` None asks for the
+    compute type of the runtime (bfloat16 when serving, float32 on the 32-bit path)."""
 
     shape: Tuple[int, ...]
-    dtype: torch.dtype = torch.float32
+    dtype: Optional[torch.dtype] = torch.float32
 
 
 @dataclass
@@ -199,8 +207,10 @@ class RunMemory:
 
     planes: Tuple[torch.Tensor, ...] = ()       # one [pages, heads, PAGE, width] tensor per plane of the mixer's CacheNeed
     page_table: Optional[torch.Tensor] = None   # [slots, max_pages] int32
-    state: Optional[torch.Tensor] = None        # [slots, *StateNeed.shape]
+    state: Optional[torch.Tensor] = None        # [slots, *StateNeed.shape]: the mixer's own
     writes: bool = True                         # False when reading another run's memory
+    # State of the block's other parts, by the role each plays in the block ("conv": ...).
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)
 
     @property
     def k_pages(self) -> Optional[torch.Tensor]:
@@ -309,6 +319,19 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class ShortConvolution(Part):
+    """A causal convolution over a few rows of each sequence, channel by channel.  Its
+    state (the last inputs of every sequence) lives in the cache like a mixer's."""
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, h: torch.Tensor, out: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor], writes: bool = True) -> None:
+        """out = conv(h) for the rows of the step, each sequence continuing from ``state``;
+        rows of padding sequences (slot -1) change nothing that outlives the step."""
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         """residual[:rows] += f(x)."""
@@ -333,30 +356,47 @@ class Head(Part):
 
 class Block(Part):
     """Arranges parts around the residual stream.  ``ROLES`` names the parts a block is
-    made of and the registry that builds each; a LayerSpec must give exactly these.  The
+    made of and the registry that builds each; a LayerSpec must give exactly these, save
+    those of ``OPTIONAL``, which a layer may leave out (the attribute is then None).  The
     built parts are attributes of the block under their role names."""
 
     ROLES: Dict[str, Registry] = {}
+    OPTIONAL: Tuple[str, ...] = ()
 
     def __init__(self, parts: Mapping[str, Part], hidden_size: int):
         super().__init__()
         self.parts: Dict[str, Part] = dict(parts)
         self.hidden_size = hidden_size
+        for role in self.OPTIONAL:
+            setattr(self, role, None)
         for role, part in self.parts.items():
             setattr(self, role, part)
 
     @classmethod
     def build(cls, spec: LayerSpec, hidden_size: int) -> "Block":
-        missing = [r for r in cls.ROLES if r not in spec.parts]
+        missing = [r for r in cls.ROLES if r not in spec.parts and r not in cls.OPTIONAL]
         unexpected = [r for r in spec.parts if r not in cls.ROLES]
         if missing or unexpected:
             raise ValueError(f"block '{spec.block}' is made of {sorted(cls.ROLES)}; missing {sorted(missing)}, unexpected {sorted(unexpected)}")
-        return cls({role: cls.ROLES[role].get(spec.parts[role].kind)(**dict(spec.parts[role].params)) for role in cls.ROLES}, hidden_size)
+        return cls({role: cls.ROLES[role].get(spec.parts[role].kind)(**dict(spec.parts[role].params))
+                    for role in cls.ROLES if role in spec.parts}, hidden_size)
 
     def named_parts(self, spec: LayerSpec):
         """(tensor-name prefix, part) of every part of this block, in the order of ROLES."""
         for role in self.ROLES:
-            yield spec.parts[role].prefix, self.parts[role]
+            if role in self.parts:
+                yield spec.parts[role].prefix, self.parts[role]
+
+    def state_needs(self) -> Dict[str, StateNeed]:
+        """Per-sequence state that parts of this block other than its mixer want, by role;
+        a run of the block finds each in ``RunMemory.states``."""
+        return {}
+
+    def rollback_states(self, states: Mapping[str, torch.Tensor], slot: int, length: int) -> bool:
+        """Like ``Mixer.rollback_state`` for the state of ``state_needs``: True if every one
+        was put back to what it was after ``length`` positions.  A block without such state
+        has nothing to put back."""
+        return not states
 
     def memory_part(self) -> Optional[Mixer]:
         """The part whose cache_need() / state_need() the cache serves for a run of this

@@ -13,16 +13,16 @@ from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, StepContext, Tens
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab_size: int, hidden_size: int):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size)
-        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, tensor: str = "weight"):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor)
+        self.vocab_size, self.hidden_size, self.tensor = int(vocab_size), int(hidden_size), str(tensor)
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor].contiguous()
 
     def forward(self, ctx: StepContext, residual: torch.Tensor) -> None:
         ops.embed(self.weight, ctx.tokens[: residual.shape[0]], residual)
@@ -36,17 +36,17 @@ class LinearHead(Head):
     """Scores = x W^T in float32.  A tied head has no tensor of its own and multiplies by
     the embedding table (model.rs:200); a folder that still stores one is tolerated."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied)
-        self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, tensor: str = "weight"):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied, tensor=tensor)
+        self.vocab_size, self.hidden_size, self.tied, self.tensor = int(vocab_size), int(hidden_size), bool(tied), str(tensor)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.vocab_size, self.hidden_size), optional=self.tied)}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size), optional=self.tied)}
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
-        self.weight = None if self.tied else tensors["weight"].contiguous()
+        self.weight = None if self.tied else tensors[self.tensor].contiguous()
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, tied: Optional[torch.Tensor]) -> None:
         w = tied if self.tied else self.weight

@@ -13,16 +13,19 @@ from .base import NORMS, Norm, Runtime, TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float):
-        super().__init__(size=size, eps=eps)
-        self.size, self.eps = int(size), float(eps)
+    """``tensor`` is the name the weight carries after the part's prefix ("weight" in
+    published Llama folders; other formats name the norm itself)."""
+
+    def __init__(self, size: int, eps: float, tensor: str = "weight"):
+        super().__init__(size=size, eps=eps, tensor=tensor)
+        self.size, self.eps, self.tensor = int(size), float(eps), str(tensor)
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), role="vector", init="ones")}
+        return {self.tensor: TensorSpec((self.size,), role="vector", init="ones")}
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.tensor]
 
     def forward(self, residual: torch.Tensor, out: torch.Tensor, gather: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(residual, self.weight, out, self.eps, gather)
