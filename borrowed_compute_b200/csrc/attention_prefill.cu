@@ -13,6 +13,11 @@
 // blocks fit an SM).  Rows are found through
 // per-sequence row ranges and start positions, so sequences of any lengths, with or
 // without earlier cached positions, share one launch.
+//
+// Keys are D wide and values DV, which may differ.  Beside the sliding window a chunk mask
+// may hold: position i sees j <= i only if both lie in the same chunk of `chunk` positions,
+// counted from the sequence's position 0 (chunk 0: none).  A step of one row a sequence runs
+// through the same kernel: the heads that share a kv head are the rows of one tile.
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
@@ -20,16 +25,16 @@
 #define AP_STAGES 2
 #define AP_ROWS 64
 
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(AP_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          const int* __restrict__ page_table, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G, int max_pages, int n_pages, int window,
-                         float scale_log2) {
-    constexpr int CHUNKS = D / 8;
-    constexpr int TILE_BYTES = 64 * D * 2;
+                         int chunk, float scale_log2) {
+    constexpr int CHUNKS = D / 8, VCHUNKS = DV / 8;
+    constexpr int K_BYTES = 64 * D * 2, TILE_BYTES = 64 * (D + DV) * 2;      // a stage: a page of keys, then its values
     constexpr int KD = D / 16;
-    constexpr int ND = D / 8;
+    constexpr int ND = DV / 8;
     extern __shared__ __align__(128) uint8_t smem[];
 
     pdl_launch_dependents();
@@ -51,6 +56,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     const int tok_end = min(n_new, tok0 + tokens_per_tile);
     const int* pages = page_table + (size_t)slot * max_pages;
 
+    // The first position a row at position p sees.
+    auto first_seen = [&](int p) {
+        int f = window > 0 && p + 1 > window ? p + 1 - window : 0;
+        if (chunk > 0) f = max(f, p / chunk * chunk);
+        return f;
+    };
     // This thread's two rows of the warp's 16: which token and head they are, and what they see.
     int tok[2], head[2], pos[2], lo[2];
     bool live[2];
@@ -61,8 +72,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         head[i] = g * group + row % group;
         live[i] = row / group < tokens_per_tile && tok[i] < n_new;
         pos[i] = start + tok[i];
-        lo[i] = window > 0 && pos[i] + 1 > window ? pos[i] + 1 - window : 0;
+        lo[i] = first_seen(pos[i]);
     }
+    // All sixteen rows of the warp see every position from the last row's first to the first row's own
+    // (the first seen position never falls as the position grows).
+    const int warp_lo = first_seen(start + tok0 + (16 * warp + 15) / group), warp_hi = start + tok0 + (16 * warp) / group;
     uint32_t qf[KD][4];
 #pragma unroll
     for (int kd = 0; kd < KD; kd++) {
@@ -76,7 +90,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     }
 
     // Pages this tile reads: from the first position its first token sees to its last token's own.
-    const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
+    const int first_pos = first_seen(start + tok0);
     const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
     const int n_tiles = t_end - t_begin;
     const int last_pos = start + n_new - 1;               // the last position the sequence holds after this step
@@ -87,12 +101,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         const int page = tile < max_pages ? pages[tile] : -1;
         if (page < 0 || page >= n_pages) return;
         const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
-        const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
-        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * DV;
+        const uint32_t kb = ad_smem(smem + (size_t)stage * TILE_BYTES), vb = kb + K_BYTES;
         for (int i = threadIdx.x; i < 64 * CHUNKS; i += AP_THREADS) {
             const int row = i / CHUNKS, c = i - row * CHUNKS;
             cp_async16(kb + tile_offset<D>(row, c), ks + (size_t)row * D + c * 8);
-            cp_async16(vb + tile_offset<D>(row, c), vs + (size_t)row * D + c * 8);
+        }
+        for (int i = threadIdx.x; i < 64 * VCHUNKS; i += AP_THREADS) {
+            const int row = i / VCHUNKS, c = i - row * VCHUNKS;
+            cp_async16(vb + tile_offset<DV>(row, c), vs + (size_t)row * DV + c * 8);
         }
     };
 
@@ -115,15 +132,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         const int tile = t_begin + it;
         const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
         if (!page_ok) continue;
-        const uint32_t kb = ad_smem(smem + (size_t)(it % AP_STAGES) * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        const uint32_t kb = ad_smem(smem + (size_t)(it % AP_STAGES) * TILE_BYTES), vb = kb + K_BYTES;
         if (tile == last_pos / BC_PAGE && last_pos % BC_PAGE != BC_PAGE - 1) {
             // The sequence's last page: what lies past its last position belongs to nobody (a
             // sequence that held the page before may have left not-a-numbers there, and 0 x NaN
             // is NaN in the product with the values): those value rows are cleared in the copy.
-            uint8_t* vt = smem + (size_t)(it % AP_STAGES) * 2 * TILE_BYTES + TILE_BYTES;
+            uint8_t* vt = smem + (size_t)(it % AP_STAGES) * TILE_BYTES + K_BYTES;
             const int first = last_pos % BC_PAGE + 1;
-            for (int i = threadIdx.x; i < (BC_PAGE - first) * CHUNKS; i += AP_THREADS)
-                *reinterpret_cast<uint4*>(vt + tile_offset<D>(first + i / CHUNKS, i % CHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
+            for (int i = threadIdx.x; i < (BC_PAGE - first) * VCHUNKS; i += AP_THREADS)
+                *reinterpret_cast<uint4*>(vt + tile_offset<DV>(first + i / VCHUNKS, i % VCHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
         }
 
@@ -144,7 +161,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         float tmax[2] = {-INFINITY, -INFINITY};
         // A page that ends at or before the position of this warp's first row is seen whole by
         // all sixteen rows (padding rows' results are never written): no mask to work out.
-        const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= start + tok0 + (16 * warp) / group;
+        const bool whole = page_ok && tile * BC_PAGE >= warp_lo && tile * BC_PAGE + BC_PAGE - 1 <= warp_hi;
         if (whole) {
 #pragma unroll
             for (int nb = 0; nb < 8; nb++)
@@ -197,7 +214,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 #pragma unroll
             for (int nd = 0; nd < ND; nd += 2) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vb + tile_offset<D>(kk * 16 + (j4 & 1) * 8 + r8, nd + (j4 >> 1)), b0, b1, b2, b3);
+                ldmatrix_x4_trans(vb + tile_offset<DV>(kk * 16 + (j4 & 1) * 8 + r8, nd + (j4 >> 1)), b0, b1, b2, b3);
                 mma_16816(o[nd], pf, b0, b1);
                 mma_16816(o[nd + 1], pf, b2, b3);
             }
@@ -210,21 +227,21 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         if (!live[i]) continue;
         const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
-        bf16* dst = out + ((size_t)(row0 + tok[i]) * H + head[i]) * D + 2 * tq;
+        bf16* dst = out + ((size_t)(row0 + tok[i]) * H + head[i]) * DV + 2 * tq;
 #pragma unroll
         for (int nd = 0; nd < ND; nd++)
             *reinterpret_cast<uint32_t*>(dst + nd * 8) = pack_bf16(o[nd][2 * i] * inv, o[nd][2 * i + 1] * inv);
     }
 }
 
-template <int D>
+template <int D, int DV>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
-                  int window, float scale, cudaStream_t s) {
-    constexpr int SMEM = AP_STAGES * 2 * 64 * D * 2;
+                  int window, int chunk, float scale, cudaStream_t s) {
+    constexpr int SMEM = AP_STAGES * 64 * (D + DV) * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
             bc_set_error("attention_prefill: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
             return (int)e;
@@ -233,8 +250,8 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     }
     const int tokens_per_tile = AP_ROWS / (H / G);
     dim3 grid(G, (max_new + tokens_per_tile - 1) / tokens_per_tile, seqs);
-    bc_launch(attention_prefill_kernel<D>, grid, dim3(AP_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
-              (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window,
+    bc_launch(attention_prefill_kernel<D, DV>, grid, dim3(AP_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
+              (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk,
               scale * 1.4426950408889634f);
     BC_LAUNCH_STATUS();
 }
@@ -257,11 +274,37 @@ extern "C" int bc_attention_prefill_bf16(const void* q, int q_stride, const void
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
     if (seqs == 0 || max_new == 0) return BC_OK;
 #define AP_CASE(DD) \
-    case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s);
+    case DD: return launch<DD, DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, 0, scale, s);
     switch (D) {
         AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
     }
 #undef AP_CASE
     bc_set_error("attention_prefill: no kernel for head size %d", D);
+    return BC_ERR_ARG;
+}
+
+// The same with values of their own width DV and a chunk mask beside the window (0: none).  Key widths 32, 64, 128
+// with value widths 16, 32, 64, 128, and every equal pair the kernel above takes.
+extern "C" int bc_attention_prefill_kv_accepts(int H, int G, int D, int DV) {
+    if (!(G > 0 && H % G == 0 && H / G <= AP_ROWS)) return 0;
+    if (D == DV) return D % 16 == 0 && D >= 16 && D <= 128;
+    return (D == 32 || D == 64 || D == 128) && (DV == 16 || DV == 32 || DV == 64 || DV == 128);
+}
+
+extern "C" int bc_attention_prefill_kv_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                            const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
+                                            int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
+                                            cudaStream_t s) {
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && max_new < 65535, "attention_prefill: bad sizes seqs=%d max_new=%d", seqs, max_new);
+    BC_CHECK_ARG(bc_attention_prefill_kv_accepts(H, G, D, DV), "attention_prefill: H=%d G=%d D=%d DV=%d is outside what this kernel takes", H, G, D, DV);
+    BC_CHECK_ARG(window >= 0 && chunk >= 0, "attention_prefill: bad window %d or chunk %d", window, chunk);
+    BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
+    if (seqs == 0 || max_new == 0) return BC_OK;
+#define AP_KV(DD, VV) \
+    if (D == DD && DV == VV) return launch<DD, VV>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, s);
+    AP_KV(16, 16) AP_KV(32, 32) AP_KV(48, 48) AP_KV(64, 64) AP_KV(80, 80) AP_KV(96, 96) AP_KV(112, 112) AP_KV(128, 128)
+    AP_KV(32, 16) AP_KV(32, 64) AP_KV(32, 128) AP_KV(64, 16) AP_KV(64, 32) AP_KV(64, 128) AP_KV(128, 16) AP_KV(128, 32) AP_KV(128, 64)
+#undef AP_KV
+    bc_set_error("attention_prefill: no kernel for key width %d with value width %d", D, DV);
     return BC_ERR_ARG;
 }

@@ -787,6 +787,38 @@ def attention_prefill_accepts(heads: int, kv_heads: int, head_dim: int, dtype: t
     return dtype == torch.bfloat16 and bool(_fn("bc_attention_prefill_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)))
 
 
+def attention_tiles_accepts(heads: int, kv_heads: int, head_dim: int, value_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tiled kernel takes keys of ``head_dim`` with values of ``value_dim`` (bf16; equal widths in
+    multiples of 16 up to 128, or keys of 32, 64, 128 with values of 16, 32, 64, 128)."""
+    return dtype == torch.bfloat16 and bool(_fn("bc_attention_prefill_kv_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                                                                                  _c_int(value_dim)))
+
+
+def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                    seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
+                    heads: int, kv_heads: int, head_dim: int, value_dim: int, window: int = 0, chunk: int = 0,
+                    scale: Optional[float] = None) -> None:
+    """Causal attention of every sequence's new rows (many, or one) against its cached positions on mma.sync
+    tiles, bf16, with values of their own width, a sliding window and/or a chunk mask (``chunk`` > 0: a position
+    sees only those of its own chunk of that many positions, counted from position 0)."""
+    for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (out, "out")):
+        _need(t, name, torch.bfloat16)
+    for t, name in ((page_table, "page_table"), (seq_rows, "seq_rows"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
+        _need(t, name, torch.int32)
+    if out.shape[1] != heads * value_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * value_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], kv_heads, PAGE, value_dim):
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    _bounds("attention_tiles: seq_slot", seq_slot, page_table.shape[0], seqs, lowest=-1)
+    _bounds("attention_tiles: seq_rows", seq_rows, out.shape[0] + 1, seqs + 1)
+    _bounds("attention_tiles: page_table", page_table, k_cache.shape[0], lowest=-1)
+    _call(_fn("bc_attention_prefill_kv_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
+          _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+          _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+
+
 def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0) -> bool:
     """Whether the tcgen05 prompt kernel takes these sizes (head size 64 or 128, at most 128
     heads a kv head) and, if given, this q (16-byte aligned, row stride a multiple of 8)."""

@@ -26,6 +26,9 @@ from . import products
 from .base import MIXERS, POSITION_ENCODINGS, CacheNeed, Mixer, RunMemory, Runtime, StepContext, TensorSpec
 
 
+force_rows = False      # tests: take the one-warp-a-row kernel (the checked twin) for bfloat16 too
+
+
 @MIXERS.register("gqa_attention_kv")
 class GroupedQueryAttentionKV(Mixer):
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, head_dim: int, value_dim: int, position: Mapping[str, Any],
@@ -85,5 +88,10 @@ class GroupedQueryAttentionKV(Mixer):
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         H, G, D, DV = self.heads, self.kv_heads, self.head_dim, self.value_dim
+        if not force_rows and ops.attention_tiles_accepts(H, G, D, DV, q.dtype):
+            # Tensor-core tiles, for prompts and for single rows alike: the heads of a kv head share every page read.
+            ops.attention_tiles(q, H * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot, ctx.seq_start, out,
+                                ctx.seqs, ctx.max_new, H, G, D, DV, window=self.window, chunk=self.chunk, scale=self.scale)
+            return
         ops.attention_rows(q, H * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out, H, G, D,
                            window=self.window, scale=self.scale, value_dim=DV, chunk=self.chunk)
