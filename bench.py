@@ -433,6 +433,163 @@ def bench_3b(pk, rng) -> dict:
     return res
 
 
+# ------------------------------------------------------------------- the second architecture
+def fegidra_config(width, heads, kv_heads, dim, vdim, chunk, delta_heads, delta_dim, rank, ff, vocab, layers):
+    """``layers`` layers of the Fegidra design, delta-rule and attention layers in turn."""
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer, kind = {"heads": delta_heads, "dim": delta_dim, "decay_rank": rank}, "general_delta"
+        else:
+            mixer, kind = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk},
+                           "rot": {"dims": dim // 2, "base": 500000.0}, "scale": 1.0 / dim ** 0.5}, "attention"
+        out.append({"type": kind, "mixer": mixer, "mlp": {"ff": ff, "kind": "dense"}})
+    return {"architecture": "Fegidra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": out}
+
+
+def llama_like(width, heads, kv_heads, dim, ff, vocab, layers):
+    return {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": layers, "hidden_size": width, "num_attention_heads": heads,
+            "num_key_value_heads": kv_heads, "head_dim": dim, "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 500000.0,
+            "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192}
+
+
+FEGIDRA_SIZES = {
+    # the width, heads and feed-forward of the 8B shape; delta heads of 64 channels; chunks of 1,024 positions
+    "wide": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=1024, delta_heads=64, delta_dim=64, rank=64, ff=14336, vocab=32000),
+    # a 2,048-wide model with values half as wide as keys
+    "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=64, chunk=512, delta_heads=32, delta_dim=64, rank=32, ff=8192, vocab=32000),
+}
+
+
+def fegidra_costs(c, layers, batch, ctx_len, T) -> dict:
+    """What each kernel class of the Fegidra model has to move in a decode step (bytes) and to compute in a
+    prompt step of T tokens (operations, or bytes where it only moves data), summed over the model's layers.
+    Half of the layers are delta-rule layers, half attention layers."""
+    E, H, G, D, DV, C = c["width"], c["heads"], c["kv_heads"], c["dim"], c["vdim"], c["chunk"]
+    HD, rank, F, V = c["delta_heads"] * c["delta_dim"], c["rank"], c["ff"], c["vocab"]
+    nd, na, B = (layers + 1) // 2, layers // 2, batch
+    n_in, n_qkv = 5 * HD + rank, H * D + G * D + G * DV
+    seen_decode = min(ctx_len % C + 1, ctx_len + 1)                     # keys a decoded row reads
+    seen_prefill = sum(min(t % C, t) + 1 for t in range(T))            # (query, key) pairs of a prompt
+    state = c["delta_heads"] * c["delta_dim"] ** 2 * 4.0
+    decode = {
+        "norm": (2 * layers + 1) * (B * E * 6.0 + E * 4.0),
+        "short convolution": layers * B * E * 2.0 * (2 + 2 * 3),
+        "delta projections": nd * (2.0 * n_in * E + B * (2.0 * E + 4.0 * n_in)),
+        "delta rule": nd * B * (2.0 * state + 4.0 * (n_in + 5 * HD) + 2.0 * HD),
+        "qkv product": na * (2.0 * n_qkv * E + B * (2.0 * E + 4.0 * n_qkv)),
+        "rotary + append": na * B * (4.0 * n_qkv + 2.0 * n_qkv),
+        "attention": na * B * (seen_decode * G * (D + DV) * 2.0 + 2.0 * H * (D + DV)),
+        "output product": nd * (2.0 * HD * E + B * (2.0 * HD + 8.0 * E)) + na * (2.0 * H * DV * E + B * (2.0 * H * DV + 8.0 * E)),
+        "up product": layers * (2.0 * E * F + B * (2.0 * E + 4.0 * F)),
+        "activation": layers * B * F * 6.0,
+        "down product": layers * (2.0 * E * F + B * (2.0 * F + 8.0 * E)),
+        "head product": 2.0 * V * E + B * (2.0 * E + 4.0 * V),
+    }
+    prefill = {
+        "norm": ("bytes", 2 * layers * T * E * 6.0),
+        "short convolution": ("bytes", layers * T * E * 4.0),
+        "delta projections": ("flops", nd * 2.0 * T * n_in * E),
+        # a step of the recurrence: two sums over the old state and its update, 11 operations a state element
+        "delta rule": ("flops32", nd * T * c["delta_heads"] * c["delta_dim"] ** 2 * 11.0),
+        "qkv product": ("flops", na * 2.0 * T * n_qkv * E),
+        "rotary + append": ("bytes", na * T * (4.0 * n_qkv + 2.0 * n_qkv)),
+        "attention": ("flops", na * 2.0 * H * (D + DV) * seen_prefill),
+        "output product": ("flops", nd * 2.0 * T * HD * E + na * 2.0 * T * H * DV * E),
+        "up product": ("flops", layers * 2.0 * T * E * F),
+        "activation": ("bytes", layers * T * F * 6.0),
+        "down product": ("flops", layers * 2.0 * T * E * F),
+    }
+    return {"decode": decode, "prefill": prefill}
+
+
+def _against(costs, measured, pk, fp32_tflops):
+    out = {}
+    for cls, m in sorted(measured.items(), key=lambda kv: -kv[1]["us"]):
+        row = {"us": round(m["us"], 1), "launches": round(m["launches"], 1)}
+        cost = costs.get(cls)
+        if cost is not None:
+            kind, amount = cost if isinstance(cost, tuple) else ("bytes", cost)
+            rate = amount / (m["us"] * 1e-6)
+            if kind == "bytes":
+                row.update({"gb_s": round(rate / 1e9, 1), "frac": round(rate / 1e9 / pk["hbm_gbs"], 3), "of": "copy rate"})
+            elif kind == "flops":
+                row.update({"tflops": round(rate / 1e12, 1), "frac": round(rate / 1e12 / pk["bf16_tflops"], 3), "of": "bf16 product rate"})
+            else:
+                row.update({"tflops": round(rate / 1e12, 2), "frac": round(rate / 1e12 / fp32_tflops, 3), "of": "float32 CUDA-core rate"})
+        out[cls] = row
+    return out
+
+
+def bench_fegidra(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
+    """Prompt and decode throughput of a Fegidra model of ``layers`` layers at sizes that resemble a real model's
+    layers (random weights), beside a Llama model of the same width, heads, feed-forward width, vocabulary and
+    depth, and every kernel class of both against its own bytes or operations (eager steps, events around
+    every launch).  Inputs exceed the L2: a step reads hundreds of MB of weights."""
+    import torch
+
+    from borrowed_compute_b200.engine import Engine, StepEntry, StepProfile
+
+    c = FEGIDRA_SIZES[size]
+    # 128 float32 lanes an SM, one fused multiply-add a clock each, at the clock the part sustains (nominal 1.965 GHz)
+    fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+    configs = {"fegidra": fegidra_config(layers=layers, **c),
+               "llama": llama_like(c["width"], c["heads"], c["kv_heads"], c["dim"], c["ff"], c["vocab"], layers)}
+    out = {"size": size, "sizes": c, "layers": layers, "batch": batch, "prompt": prompt,
+           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(fp32_tflops, 1)}
+    for name, cfg in configs.items():
+        eng = Engine.from_random(cfg, seed=1, max_tokens=batch * (prompt + 256), max_slots=batch, max_seq=prompt + 256)
+        vocab = c["vocab"]
+        prompts = [[int(t) for t in rng.integers(0, vocab, prompt)] for _ in range(batch)]
+        res = timed_decode(eng, prompts, steps, warmup, rng, vocab, prompts_a_step=batch)
+        # one prompt alone, timed on the device over three runs after a warm-up
+        slot = eng.acquire()
+        times = []
+        for i in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([StepEntry(slot, prompts[0], want=(prompt - 1,))])
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            eng.rollback(slot, 0)
+        prompt_ms = statistics.median(times[1:])
+        # every class, launch by launch
+        slots = [slot] + [eng.acquire() for _ in range(batch - 1)]
+        eng.step([StepEntry(s, p, want=()) for s, p in zip(slots, prompts)])
+        one = lambda: eng.step([StepEntry(s, (int(rng.integers(0, vocab)),), want=(0,)) for s in slots])   # noqa: E731
+        with StepProfile(eng):
+            one()
+        with StepProfile(eng) as prof:
+            for _ in range(3):
+                one()
+        decode_classes = prof.classes(3)
+        for s in slots:
+            eng.release(s)
+        slot = eng.acquire()
+        with StepProfile(eng):
+            eng.step([StepEntry(slot, prompts[0], want=(prompt - 1,))])
+        eng.rollback(slot, 0)
+        with StepProfile(eng) as prof:
+            eng.step([StepEntry(slot, prompts[0], want=(prompt - 1,))])
+        prefill_classes = prof.classes(1)
+        eng.release(slot)
+        eng.raise_on_kernel_error()
+        costs = fegidra_costs(c, layers, batch, prompt + 2, prompt) if name == "fegidra" else class_costs(cfg, layers, batch, batch * (prompt + 2), prompt)
+        out[name] = {
+            "decode_ms_per_step": round(res["ms_per_step"], 4), "decode_tok_s": round(res["tok_s"], 1),
+            "prompt_ms": round(prompt_ms, 3), "prompt_tok_s": round(prompt / (prompt_ms / 1000.0), 1),
+            "batch_prompt_tok_s": round(batch * prompt / (res["prompt_ms"] / 1000.0), 1),
+            "weight_bytes": eng.weight_bytes(),
+            "decode_classes": _against(costs["decode"], decode_classes, pk, fp32_tflops),
+            "prefill_classes": _against(costs["prefill"], prefill_classes, pk, fp32_tflops),
+        }
+        del eng
+        free_device_memory()
+    return out
+
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -591,8 +748,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
-    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny"],
+    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra"],
                     help="run one of the further workloads alone and print its figures (not the contract's line)")
+    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra: which sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "
@@ -608,7 +766,8 @@ def main() -> int:
 
         rng = np.random.default_rng(0)
         one = {"long": lambda: bench_long(peaks(), rng, args.layers), "13b": lambda: bench_13b(peaks(), rng), "3b": lambda: bench_3b(peaks(), rng),
-               "tiny": lambda: bench_tiny(rng)}[args.point]
+               "tiny": lambda: bench_tiny(rng),
+               "fegidra": lambda: bench_fegidra(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
         print(json.dumps({"point": args.point, **one()}))
         return 0
     print(json.dumps(run_ours(args)))

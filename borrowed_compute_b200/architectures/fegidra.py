@@ -22,7 +22,7 @@ NO_LIMIT = 1 << 20
 
 
 def fegidra_model_spec(cfg: FegidraConfig) -> ModelSpec:
-    layers = []
+    layers, tolerated = [], []
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         parts = {"norm1": PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps, "tensor": "norm1"}, p)}
@@ -41,6 +41,8 @@ def fegidra_model_spec(cfg: FegidraConfig) -> ModelSpec:
         if layer.ff > 0:
             parts["norm2"] = PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps, "tensor": "norm2"}, p)
             parts["feed_forward"] = PartSpec("polynorm_mlp", {"hidden_size": cfg.width, "intermediate_size": layer.ff, "eps": cfg.norm_eps}, p + "mlp.")
+        else:
+            tolerated.append((p + "norm2", (cfg.width,)))      # the norm of the branch this layer leaves out
         layers.append(LayerSpec("parallel", parts))
     return ModelSpec(
         hidden_size=cfg.width,
@@ -51,6 +53,7 @@ def fegidra_model_spec(cfg: FegidraConfig) -> ModelSpec:
         schedule=tuple(RunSpec(i) for i in range(len(layers))),
         final_norm=PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps, "tensor": "norm"}, "final."),
         head=PartSpec("linear_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tensor": "head"}, ""),
+        tolerated=tuple(tolerated),
     )
 
 

@@ -51,6 +51,13 @@ template <> struct KeyDot<bf16> {
     }
 };
 
+// Head sizes that are no multiple of 8: element by element, in the same ascending order.
+template <class T> __device__ __forceinline__ float dot_any(const T* k, const float* q, int D) {
+    float s = 0.0f;
+    for (int d = 0; d < D; d++) s = fmaf(to_f32(k[d]), q[d], s);
+    return s;
+}
+
 template <class T>
 __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
                                                                    const T* __restrict__ v_cache, const int* __restrict__ page_table,
@@ -94,7 +101,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
         const int t = t0 + lane;
         const bool seen = page >= 0 && t >= lo && t <= pos;
         float s = -INFINITY;
-        if (seen) s = KeyDot<T>::dot(k_cache + base + (size_t)lane * D, qs[warp], D) * scale;
+        if (seen) s = (D % 8 == 0 ? KeyDot<T>::dot(k_cache + base + (size_t)lane * D, qs[warp], D) : dot_any<T>(k_cache + base + (size_t)lane * D, qs[warp], D)) * scale;
         const float mn = fmaxf(m, warp_max(s));
         const float corr = mn == -INFINITY ? 1.0f : expf(m - mn);
         const float p = seen ? expf(s - mn) : 0.0f;
@@ -126,7 +133,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk,
                   float scale, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && H > 0 && G > 0 && H % G == 0, "attention_rows: bad sizes rows=%d H=%d G=%d", rows, H, G);
-    BC_CHECK_ARG(D > 0 && D % 8 == 0 && D <= MAX_D, "attention_rows: head size %d is not a multiple of 8 up to %d", D, MAX_D);
+    BC_CHECK_ARG(D > 0 && D <= MAX_D, "attention_rows: head size %d is not within 1 to %d", D, MAX_D);
     BC_CHECK_ARG(DV > 0 && DV <= MAX_D && window >= 0 && chunk >= 0, "attention_rows: bad value width %d, window %d or chunk %d", DV, window, chunk);
     BC_CHECK_ARG(rows <= 2147483647 && (H + WARPS - 1) / WARPS <= 65535, "attention_rows: too many heads (%d)", H);
     if (rows == 0) return BC_OK;

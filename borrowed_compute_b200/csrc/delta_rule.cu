@@ -14,7 +14,8 @@
 //              o_j  = r . s_j' = (r*w) . s_j - (r.(a*u)) (u . s_j) + (r.k) v_j,
 //            so one pass over the old column gives both sums.  Eight threads share a column
 //            (D/8 key channels each, in registers) and add their sums by shuffles; the
-//            step's vectors are staged in shared memory sixteen rows at a time;
+//            step's vectors are staged in shared memory sixteen rows at a time (eight for
+//            heads wider than 128);
 //   finish   (row, head) in parallel: the head's output divided by its root mean square,
 //            times a weight, times the sigmoid of a gate.
 //
@@ -25,8 +26,7 @@
 
 #define DR_LANES 8          // threads that share one value channel
 #define DR_COLS 16          // value channels a block
-#define DR_STEPS 16         // rows staged at a time
-#define DR_MAX_D 128
+#define DR_MAX_D 256
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -73,7 +73,7 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, int stride,
     }
 }
 
-template <int R>   // key channels a thread: D <= 8 R
+template <int R, int DR_STEPS>   // key channels a thread (D <= 8 R) and rows staged at a time
 __global__ void __launch_bounds__(DR_LANES * DR_COLS)
 delta_scan_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ decay, const float* __restrict__ unit,
                   const float* __restrict__ removal, const float* __restrict__ dots, float* __restrict__ state,
@@ -167,6 +167,127 @@ __global__ void delta_finish_kernel(const float* __restrict__ o, const float* __
     if (mine) out[(size_t)row * HD + c] = from_f32<T>(v * scale * weight[c] * sigmoid_f(gate[(size_t)row * gate_stride + c]));
 }
 
+// A step of one row a sequence: prepare, one step of the scan and finish in one launch, a block a (row, head)
+// with eight threads a value channel.  Every sum is taken by the same threads in the same order as in the three
+// kernels above (thread d holds channel d in the sums over a head), so a row decoded alone and the same row in a
+// prompt give the same bits.  Heads of up to 128 channels.
+template <int R, class T>
+__global__ void __launch_bounds__(64 * R)
+delta_step_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ w2, const float* __restrict__ w0,
+                  const float* __restrict__ a_bias, const float* __restrict__ norm_w, float* __restrict__ state,
+                  const int* __restrict__ row_slot, T* __restrict__ out, int H, int D, int inner, float decay_scale, float key_eps,
+                  float norm_eps, int n_slots, int write_state) {
+    constexpr int DP = DR_LANES * R;
+    extern __shared__ float sm[];
+    __shared__ float scratch[32];
+    float* th = sm;
+    float* sw = th + ((inner + 3) & ~3);
+    float *su = sw + DP, *sb = su + DP, *sr = sb + DP, *sk = sr + DP, *so = sk + DP;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, head = blockIdx.y, HD = H * D;
+    const int slot = row_slot[row];
+    if (slot < 0 || slot >= n_slots) return;
+    const float* p = proj + (size_t)row * stride;
+    for (int j = threadIdx.x; j < inner; j += blockDim.x) th[j] = tanhf(p[5 * HD + j]);
+    __syncthreads();
+    const int d = threadIdx.x, c = head * D + d;
+    const bool mine = d < D;
+    float r = 0.0f, k = 0.0f, a = 0.0f, w = 0.0f;
+    if (mine) {
+        r = p[c];
+        k = p[HD + c];
+        a = sigmoid_f(p[4 * HD + c] + a_bias[c]);
+        float z = 0.0f;
+        const float* wr = w2 + (size_t)c * inner;
+        for (int j = 0; j < inner; j++) z = fmaf(wr[j], th[j], z);
+        w = expf(-decay_scale * sigmoid_f(z + w0[c]));
+    }
+    const float kk = block_sum(k * k, scratch);
+    const float u = k / sqrtf(kk + key_eps);
+    const float au = a * u;
+    const float r_au = block_sum(r * au, scratch);
+    const float r_k = block_sum(r * k, scratch);
+    if (d < DP) {
+        sw[d] = mine ? w : 0.0f;
+        su[d] = mine ? u : 0.0f;
+        sb[d] = mine ? au : 0.0f;
+        sr[d] = mine ? r : 0.0f;
+        sk[d] = mine ? k : 0.0f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x % DR_LANES, j = threadIdx.x / DR_LANES;
+    const bool col_ok = j < D;
+    float* S = state + ((size_t)slot * H + head) * D * D;
+    float s[R];
+#pragma unroll
+    for (int q = 0; q < R; q++) {
+        const int i = lane * R + q;
+        s[q] = col_ok && i < D ? S[(size_t)i * D + j] : 0.0f;
+    }
+    float rws = 0.0f, us = 0.0f;
+#pragma unroll
+    for (int q = 0; q < R; q++) {
+        const int i = lane * R + q;
+        rws = fmaf(sr[i] * sw[i], s[q], rws);
+        us = fmaf(su[i], s[q], us);
+    }
+#pragma unroll
+    for (int o = DR_LANES / 2; o > 0; o >>= 1) {
+        rws += __shfl_xor_sync(0xffffffffu, rws, o);
+        us += __shfl_xor_sync(0xffffffffu, us, o);
+    }
+    const float v = col_ok ? p[2 * HD + (size_t)head * D + j] : 0.0f;
+    if (write_state) {
+#pragma unroll
+        for (int q = 0; q < R; q++) {
+            const int i = lane * R + q;
+            if (col_ok && i < D) S[(size_t)i * D + j] = fmaf(sk[i], v, fmaf(-sb[i], us, sw[i] * s[q]));
+        }
+    }
+    if (lane == 0 && col_ok) so[j] = fmaf(r_k, v, fmaf(-r_au, us, rws));
+    __syncthreads();
+    const float o = mine ? so[d] : 0.0f;
+    const float ss = block_sum(o * o, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)D + norm_eps);
+    if (mine) out[(size_t)row * HD + c] = from_f32<T>(o * scale * norm_w[c] * sigmoid_f(p[3 * HD + c]));
+}
+
+template <class T>
+static int step(const float* proj, int stride, const float* w2, const float* w0, const float* a_bias, const float* norm_w, float* state,
+                const int* row_slot, void* out, int rows, int H, int D, int inner, float decay_scale, float key_eps, float norm_eps, int n_slots,
+                int write_state, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && H > 0 && H <= 65535 && D > 0 && D <= 128 && inner > 0 && inner <= 8192,
+                 "delta_step: bad sizes rows=%d H=%d D=%d inner=%d (a head of at most 128)", rows, H, D, inner);
+    BC_CHECK_ARG(stride >= 5 * H * D + inner, "delta_step: a row of %d values cannot hold five projections of %d and %d more", stride, H * D, inner);
+    if (rows == 0) return BC_OK;
+    const int threads = DR_LANES * ((D + 3) / 4 * 4);
+    const dim3 grid(rows, H);
+#define DS_CASE(R)                                                                                                                         \
+    bc_launch(delta_step_kernel<R, T>, grid, dim3(threads), (size_t)(((inner + 3) & ~3) + 5 * DR_LANES * R + D) * sizeof(float), s, proj, \
+              stride, w2, w0, a_bias, norm_w, state, row_slot, (T*)out, H, D, inner, decay_scale, key_eps, norm_eps, n_slots, write_state)
+    if (D <= 16) DS_CASE(2);
+    else if (D <= 32) DS_CASE(4);
+    else if (D <= 64) DS_CASE(8);
+    else DS_CASE(16);
+#undef DS_CASE
+    BC_LAUNCH_STATUS();
+}
+// One row a sequence (row r lives in slot row_slot[r]; negative: skipped, its row of `out` is left untouched):
+// proj as for bc_delta_prepare, state as for bc_delta_scan, out [rows, H D] as from bc_delta_finish.
+extern "C" int bc_delta_step_f32(const float* proj, int stride, const float* w2, const float* w0, const float* a_bias, const float* norm_w,
+                                 float* state, const int* row_slot, void* out, int rows, int H, int D, int inner, float decay_scale,
+                                 float key_eps, float norm_eps, int n_slots, int write_state, cudaStream_t s) {
+    return step<float>(proj, stride, w2, w0, a_bias, norm_w, state, row_slot, out, rows, H, D, inner, decay_scale, key_eps, norm_eps, n_slots,
+                       write_state, s);
+}
+extern "C" int bc_delta_step_bf16(const float* proj, int stride, const float* w2, const float* w0, const float* a_bias, const float* norm_w,
+                                  float* state, const int* row_slot, void* out, int rows, int H, int D, int inner, float decay_scale,
+                                  float key_eps, float norm_eps, int n_slots, int write_state, cudaStream_t s) {
+    return step<bf16>(proj, stride, w2, w0, a_bias, norm_w, state, row_slot, out, rows, H, D, inner, decay_scale, key_eps, norm_eps, n_slots,
+                      write_state, s);
+}
+
 static int threads_for(int D) { return ((D + 31) / 32) * 32; }
 
 extern "C" int bc_delta_prepare(const float* proj, int stride, const float* w2, const float* w0, const float* a_bias, float* decay, float* unit,
@@ -191,13 +312,14 @@ extern "C" int bc_delta_scan(const float* proj, int stride, const float* decay, 
                  "delta_scan: bad sizes seqs=%d H=%d D=%d (a head of at most %d)", seqs, H, D, DR_MAX_D);
     if (seqs == 0) return BC_OK;
     const dim3 grid(seqs, H, (D + DR_COLS - 1) / DR_COLS), block(DR_LANES * DR_COLS);
-#define DR_CASE(R)                                                                                                                      \
-    bc_launch(delta_scan_kernel<R>, grid, block, 0, s, proj, stride, decay, unit, removal, dots, state, seq_rows, seq_slot, out, H, D, \
+#define DR_CASE(R, STEPS)                                                                                                                      \
+    bc_launch(delta_scan_kernel<R, STEPS>, grid, block, 0, s, proj, stride, decay, unit, removal, dots, state, seq_rows, seq_slot, out, H, D, \
               n_slots, write_state)
-    if (D <= 16) DR_CASE(2);
-    else if (D <= 32) DR_CASE(4);
-    else if (D <= 64) DR_CASE(8);
-    else DR_CASE(16);
+    if (D <= 16) DR_CASE(2, 16);
+    else if (D <= 32) DR_CASE(4, 16);
+    else if (D <= 64) DR_CASE(8, 16);
+    else if (D <= 128) DR_CASE(16, 16);
+    else DR_CASE(32, 8);
 #undef DR_CASE
     BC_LAUNCH_STATUS();
 }

@@ -66,6 +66,69 @@ short_conv_tail_kernel(const T* __restrict__ h, T* __restrict__ tail, const int*
     }
 }
 
+// Two RMS norms of the same row share its statistic: out1 = x / rms(x) * w1, out2 = x / rms(x) * w2
+// (out2 may be null).  With `taps` > 0 the first output also passes the convolution above, for steps of one
+// row a sequence only (row r is sequence r's one row): the sum runs over the tail and the row's own rounded
+// value in the same order as in short_conv_kernel, so both ways give the same bits; the tail moves up by one.
+template <class T>
+__global__ void __launch_bounds__(SC_THREADS)
+norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ w2, const float* __restrict__ cw,
+                      T* __restrict__ tail, const int* __restrict__ row_slot, T* __restrict__ out1, T* __restrict__ out2, int E, float eps,
+                      int taps, int n_slots, int update_tail) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)r * E;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < E; c += blockDim.x) ss += xr[c] * xr[c];
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)E + eps);
+    const int slot = taps > 0 ? row_slot[r] : -1;
+    const bool conv = taps > 0 && slot >= 0 && slot < n_slots;
+    for (int c = threadIdx.x; c < E; c += blockDim.x) {
+        const float v = xr[c];
+        const T h = from_f32<T>(v * scale * w1[c]);
+        if (out2) out2[(size_t)r * E + c] = from_f32<T>(v * scale * w2[c]);
+        if (!conv) {
+            out1[(size_t)r * E + c] = h;
+            continue;
+        }
+        T* tl = tail + (size_t)slot * (taps - 1) * E + c;
+        const float own = to_f32(h);
+        float acc = 0.0f;
+        for (int j = 0; j + 1 < taps; j++) acc = fmaf(cw[(size_t)c * taps + j], to_f32(tl[(size_t)j * E]), acc);
+        acc = fmaf(cw[(size_t)c * taps + taps - 1], own, acc);
+        out1[(size_t)r * E + c] = from_f32<T>(own + acc);
+        if (update_tail) {
+            for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
+            if (taps > 1) tl[(size_t)(taps - 2) * E] = h;
+        }
+    }
+}
+
+template <class T>
+static int launch_pair(const float* x, const float* w1, const float* w2, const float* cw, void* tail, const int* row_slot, void* out1,
+                       void* out2, int rows, int E, float eps, int taps, int n_slots, int update_tail, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && E > 0 && taps >= 0, "norm_pair: bad sizes rows=%d E=%d taps=%d", rows, E, taps);
+    BC_CHECK_ARG(taps == 0 || (cw && row_slot && (tail || taps == 1)), "norm_pair: the convolution needs its weights, the rows' slots and the tail");
+    if (rows == 0) return BC_OK;
+    bc_launch(norm_pair_conv_kernel<T>, dim3(rows), dim3(SC_THREADS), 0, s, x, w1, w2, cw, (T*)tail, row_slot, (T*)out1, (T*)out2, E, eps, taps,
+              n_slots, update_tail);
+    BC_LAUNCH_STATUS();
+}
+
+// x: [rows, E] float; w1, w2: [E] float; out1, out2: [rows, E] (out2 and w2 may be null).  taps 0: no convolution;
+// else cw [E, taps], tail [n_slots, taps - 1, E], row_slot [rows], every row being its sequence's only row of the step.
+extern "C" int bc_norm_pair_f32(const float* x, const float* w1, const float* w2, const float* cw, void* tail, const int* row_slot, void* out1,
+                                void* out2, int rows, int E, float eps, int taps, int n_slots, int update_tail, cudaStream_t s) {
+    return launch_pair<float>(x, w1, w2, cw, tail, row_slot, out1, out2, rows, E, eps, taps, n_slots, update_tail, s);
+}
+extern "C" int bc_norm_pair_bf16(const float* x, const float* w1, const float* w2, const float* cw, void* tail, const int* row_slot, void* out1,
+                                 void* out2, int rows, int E, float eps, int taps, int n_slots, int update_tail, cudaStream_t s) {
+    return launch_pair<bf16>(x, w1, w2, cw, tail, row_slot, out1, out2, rows, E, eps, taps, n_slots, update_tail, s);
+}
+
 template <class T>
 static int launch(const void* h, const float* w, void* tail, const int* seq_rows, const int* seq_slot, void* out, int seqs, int max_new,
                   int E, int taps, int n_slots, int write_tail, cudaStream_t s) {

@@ -48,6 +48,8 @@ class DecoderModel:
         for prefix, part in self.named_parts():
             for name, spec in part.tensors().items():
                 out[prefix + name] = spec
+        for name, shape in self.spec.tolerated:
+            out.setdefault(name, TensorSpec(tuple(shape), role="vector", optional=True))
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:

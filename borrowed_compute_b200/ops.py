@@ -143,7 +143,7 @@ label = ""
 _CLASS_OF = {
     "bc_embed": "embedding", "bc_rmsnorm": "norm", "bc_swiglu": "activation", "bc_rope_append": "rotary + append",
     "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
-    "bc_short_conv": "short convolution", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
+    "bc_short_conv": "short convolution", "bc_norm_pair": "norm", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
 }
 
@@ -562,6 +562,39 @@ def short_conv(h: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, seq_ro
           _c_int(seqs), _c_int(max_new), _c_int(E), _c_int(taps), _c_int(tail.shape[0]), _c_int(1 if write_tail else 0), _stream())
 
 
+def norm_pair(x: torch.Tensor, w1: torch.Tensor, w2: Optional[torch.Tensor], out1: torch.Tensor, out2: Optional[torch.Tensor], eps: float,
+              conv_weight: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None, row_slot: Optional[torch.Tensor] = None,
+              write_tail: bool = True) -> None:
+    """Two RMS norms of the same rows with one statistic: out1 = x / rms(x) * w1, out2 = x / rms(x) * w2 (the second
+    may be left out).  With ``conv_weight`` [E, taps] the first output also passes the short causal convolution of
+    ``short_conv``, for steps in which every sequence brings one row (row r belongs to slot ``row_slot[r]``); the
+    tail is brought up to date."""
+    _need(x, "x", torch.float32)
+    _need(w1, "w1", torch.float32)
+    _need(out1, "out1")
+    rows, E = x.shape
+    if w1.numel() != E or tuple(out1.shape) != (rows, E):
+        raise KernelError(f"norm_pair: x {tuple(x.shape)}, w1 {w1.numel()}, out1 {tuple(out1.shape)} do not fit")
+    if (w2 is None) != (out2 is None):
+        raise KernelError("norm_pair: the second norm needs its weight and its output")
+    if w2 is not None:
+        _need(w2, "w2", torch.float32)
+        _need(out2, "out2", out1.dtype)
+        if w2.numel() != E or out2.shape != out1.shape:
+            raise KernelError("norm_pair: the second norm's sizes differ")
+    taps, n_slots = 0, 0
+    if conv_weight is not None:
+        _need(conv_weight, "conv_weight", torch.float32)
+        _need(tail, "tail", out1.dtype)
+        _need(row_slot, "row_slot", torch.int32)
+        taps, n_slots = conv_weight.shape[1], tail.shape[0]
+        if conv_weight.shape[0] != E or tuple(tail.shape[1:]) != (taps - 1, E) or row_slot.numel() < rows:
+            raise KernelError(f"norm_pair: conv weight {tuple(conv_weight.shape)}, tail {tuple(tail.shape)} do not fit {E} channels")
+        _bounds("norm_pair: row_slot", row_slot, n_slots, rows, lowest=-1)
+    _call(_fn("bc_norm_pair_" + _suffix(out1.dtype)), _ptr(x), _ptr(w1), _ptr(w2), _ptr(conv_weight), _ptr(tail), _ptr(row_slot), _ptr(out1),
+          _ptr(out2), _c_int(rows), _c_int(E), _c_float(eps), _c_int(taps), _c_int(n_slots), _c_int(1 if write_tail else 0), _stream())
+
+
 def delta_prepare(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, decay: torch.Tensor, unit: torch.Tensor,
                   removal: torch.Tensor, dots: torch.Tensor, heads: int, head_dim: int, decay_scale: float, key_eps: float) -> None:
     """From the fused projection [rows, 5 H D + inner] (r, k, v, gate, a, decay's inner projection; float32): per key
@@ -611,6 +644,32 @@ def delta_finish(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weight: 
     gate = proj.reshape(-1)[gate_offset:]
     _call(_fn("bc_delta_finish_" + _suffix(out.dtype)), _ptr(o), _c_void_p(gate.data_ptr()), _c_int(proj.shape[1]), _ptr(weight), _ptr(out),
           _c_int(rows), _c_int(heads), _c_int(head_dim), _c_float(eps), _stream())
+
+
+def delta_step_accepts(head_dim: int) -> bool:
+    """Whether the one-launch step for single rows takes heads of this size (up to 128 channels)."""
+    return 0 < head_dim <= 128
+
+
+def delta_step(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor,
+               row_slot: torch.Tensor, out: torch.Tensor, heads: int, head_dim: int, decay_scale: float, key_eps: float, norm_eps: float,
+               write_state: bool = True) -> None:
+    """``delta_prepare``, one step of ``delta_scan`` and ``delta_finish`` in one launch, for steps in which every
+    sequence brings one row (row r lives in slot ``row_slot[r]``); the same bits as the three."""
+    for t, name in ((proj, "proj"), (w2, "w2"), (w0, "w0"), (a_bias, "a_bias"), (norm_weight, "norm_weight"), (state, "state")):
+        _need(t, name, torch.float32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(out, "out")
+    rows, stride = proj.shape
+    HD, inner = heads * head_dim, w2.shape[1]
+    if w2.shape[0] != HD or w0.numel() != HD or a_bias.numel() != HD or norm_weight.numel() != HD or stride != 5 * HD + inner:
+        raise KernelError(f"delta_step: proj {tuple(proj.shape)}, w2 {tuple(w2.shape)} do not fit {heads} heads of {head_dim}")
+    if tuple(state.shape[1:]) != (heads, head_dim, head_dim) or tuple(out.shape) != (rows, HD) or row_slot.numel() < rows:
+        raise KernelError(f"delta_step: state {tuple(state.shape)} or out {tuple(out.shape)} do not fit")
+    _bounds("delta_step: row_slot", row_slot, state.shape[0], rows, lowest=-1)
+    _call(_fn("bc_delta_step_" + _suffix(out.dtype)), _ptr(proj), _c_int(stride), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(norm_weight),
+          _ptr(state), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(head_dim), _c_int(inner), _c_float(decay_scale),
+          _c_float(key_eps), _c_float(norm_eps), _c_int(state.shape[0]), _c_int(1 if write_state else 0), _stream())
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, out: torch.Tensor, eps: float) -> None:

@@ -37,8 +37,8 @@ class GroupedQueryAttentionKV(Mixer):
                          scale=scale, window=window, chunk=chunk, bias=bias, qk_norm_eps=qk_norm_eps)
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} kv heads")
-        if head_dim % 8 or not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
-            raise ValueError(f"head size {head_dim} (a multiple of 8 up to 256) or value size {value_dim} (up to 256) is refused by the attention kernels")
+        if not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
+            raise ValueError(f"head size {head_dim} or value size {value_dim} is refused by the attention kernels (1 to 256)")
         self.hidden_size, self.heads, self.kv_heads = int(hidden_size), int(heads), int(kv_heads)
         self.head_dim, self.value_dim = int(head_dim), int(value_dim)
         self.window, self.chunk, self.bias = int(window), int(chunk), bool(bias)

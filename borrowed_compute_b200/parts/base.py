@@ -122,6 +122,9 @@ class ModelSpec:
     # ``on_embeddings``), with tensors of its own if it wants any; None for models whose
     # positions live inside their mixers (rotary tables).
     position: Optional[PartSpec] = None
+    # (name, shape) of tensors a folder may hold although no part reads them (the norm of a
+    # branch that a layer leaves out, say): tolerated when present, never asked for.
+    tolerated: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
 
 # -------------------------------------------------------------------------- declared tensors

@@ -13,6 +13,9 @@ import torch
 
 from typing import Dict, Mapping
 
+from .. import ops
+from .norm import RMSNorm
+from .short_conv import CausalConvResidual
 from .base import BLOCKS, CONVOLUTIONS, FEED_FORWARDS, MIXERS, NORMS, Block, RunMemory, Runtime, StateNeed, StepContext
 
 
@@ -38,6 +41,10 @@ class ParallelBlock(Block):
         if (self.norm2 is None) != (self.feed_forward is None):
             raise ValueError("a parallel block has a feed-forward and its norm, or neither")
 
+    def _one_statistic(self) -> bool:
+        """Whether both norms are plain RMS norms with the same eps, so that they share the row's statistic."""
+        return type(self.norm1) is RMSNorm and (self.norm2 is None or (type(self.norm2) is RMSNorm and self.norm2.eps == self.norm1.eps))
+
     def state_needs(self) -> Dict[str, StateNeed]:
         need = None if self.conv is None else self.conv.state_need()
         return {} if need is None else {"conv": need}
@@ -46,11 +53,23 @@ class ParallelBlock(Block):
         rows = residual.shape[0]
         # Both branches read the stream as it is now, so both norms run before either adds to it.
         h = torch.empty((rows, self.hidden_size), dtype=rt.dtype, device=residual.device)
-        self.norm1.forward(residual, h)
-        if self.feed_forward is not None:
-            h2 = torch.empty((rows, self.hidden_size), dtype=rt.dtype, device=residual.device)
-            self.norm2.forward(residual, h2)
-        if self.conv is not None:
+        h2 = torch.empty_like(h) if self.feed_forward is not None else None
+        if self._one_statistic():
+            # Two RMS norms of the same rows are one kernel; in a step of single rows the convolution rides in it too.
+            conv = self.conv if self.conv is not None and ctx.decode and isinstance(self.conv, CausalConvResidual) else None
+            tail = None if conv is None else mem.states.get("conv")
+            if conv is not None and tail is None:
+                raise RuntimeError("the convolution was given no state: the cache does not serve this block")
+            ops.norm_pair(residual, self.norm1.weight, None if h2 is None else self.norm2.weight, h, h2, self.norm1.eps,
+                          None if conv is None else conv.weight, None if conv is None else (tail if conv.taps > 1 else tail[:, :0]),
+                          ctx.row_slot, write_tail=mem.writes)
+            done = conv is not None
+        else:
+            self.norm1.forward(residual, h)
+            if h2 is not None:
+                self.norm2.forward(residual, h2)
+            done = False
+        if self.conv is not None and not done:
             hc = torch.empty_like(h)
             self.conv.forward(h, hc, ctx, mem.states.get("conv"), mem.writes)
             h = hc

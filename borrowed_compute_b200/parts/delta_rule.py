@@ -28,14 +28,17 @@ from . import products
 from .base import MIXERS, Mixer, RunMemory, Runtime, StateNeed, StepContext, TensorSpec
 
 
+split_steps = False      # tests: steps of single rows through the three kernels of a prompt step
+
+
 @MIXERS.register("generalized_delta")
 class GeneralizedDelta(Mixer):
     def __init__(self, hidden_size: int, heads: int, head_dim: int, decay_rank: int, norm_eps: float,
                  decay_scale: float = math.exp(-0.5), key_eps: float = 1e-6):
         super().__init__(hidden_size=hidden_size, heads=heads, head_dim=head_dim, decay_rank=decay_rank, norm_eps=norm_eps,
                          decay_scale=decay_scale, key_eps=key_eps)
-        if not 0 < int(head_dim) <= 128:
-            raise ValueError(f"a head of {head_dim} channels is outside what the recurrence kernel takes (1 to 128)")
+        if not 0 < int(head_dim) <= 256:
+            raise ValueError(f"a head of {head_dim} channels is outside what the recurrence kernel takes (1 to 256)")
         self.hidden_size, self.heads, self.head_dim, self.decay_rank = int(hidden_size), int(heads), int(head_dim), int(decay_rank)
         self.norm_eps, self.decay_scale, self.key_eps = float(norm_eps), float(decay_scale), float(key_eps)
 
@@ -65,11 +68,17 @@ class GeneralizedDelta(Mixer):
         hd, f32, dev = H * D, torch.float32, x.device
         proj = torch.empty((rows, self.w_in.shape[0]), dtype=f32, device=dev)
         products.linear(x, self.w_in, proj, products.EPI_STORE_F32, "delta projections")
+        y = torch.empty((rows, hd), dtype=x.dtype, device=dev)
+        if ctx.decode and not split_steps and ops.delta_step_accepts(D):
+            # One row a sequence: the three kernels below as one launch (the same bits).
+            ops.delta_step(proj, self.w2, self.w0, self.a_bias, self.norm_weight, mem.state, ctx.row_slot, y, H, D, self.decay_scale,
+                           self.key_eps, self.norm_eps, write_state=mem.writes)
+            products.linear(y, self.w_o, residual, products.EPI_ADD_F32, "output product")
+            return
         decay, unit, removal = (torch.empty((rows, hd), dtype=f32, device=dev) for _ in range(3))
         dots = torch.empty((rows, H, 2), dtype=f32, device=dev)
         ops.delta_prepare(proj, self.w2, self.w0, self.a_bias, decay, unit, removal, dots, H, D, self.decay_scale, self.key_eps)
         o = torch.empty((rows, hd), dtype=f32, device=dev)
         ops.delta_scan(proj, decay, unit, removal, dots, mem.state, ctx.seq_rows, ctx.seq_slot, o, ctx.seqs, H, D, write_state=mem.writes)
-        y = torch.empty((rows, hd), dtype=x.dtype, device=dev)
         ops.delta_finish(o, proj, 3 * hd, self.norm_weight, y, H, D, self.norm_eps)
         products.linear(y, self.w_o, residual, products.EPI_ADD_F32, "output product")

@@ -134,6 +134,43 @@ def test_short_convolution_whole_and_in_portions(dtype, taps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps", [0, 1, 3, 4])
+def test_two_norms_with_one_statistic_and_the_convolution_riding_along(dtype, taps):
+    """out1 = conv(norm(x) w1), out2 = norm(x) w2 for single rows of three sequences, six steps in a row,
+    against the plain norm and the plain convolution over each sequence's rows."""
+    from borrowed_compute_b200 import ops
+
+    rng, E, dev, eps = np.random.default_rng(taps + 20), 200, "cuda:0", 1e-5
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    w1, w2 = (rng.uniform(0.5, 1.5, E).astype(np.float32) for _ in range(2))
+    kernel = rng.standard_normal((E, max(taps, 1))).astype(np.float32)
+    xs = rng.standard_normal((6, 3, E)).astype(np.float32) * np.array([0.1, 1.0, 30.0], dtype=np.float32)[None, :, None]
+    slots = [3, 0, 1]
+    tail = torch.zeros((4, max(taps - 1, 1), E), dtype=td, device=dev)
+    got1, got2 = [], []
+    for step in range(6):
+        x = torch.from_numpy(xs[step]).to(dev)
+        out1, out2 = torch.empty((4, E), dtype=td, device=dev), torch.empty((4, E), dtype=td, device=dev)
+        xx = torch.cat([x, torch.ones((1, E), device=dev)])          # a padding row (slot -1) after the three
+        row_slot = torch.tensor(slots + [-1], dtype=torch.int32, device=dev)
+        if taps:
+            ops.norm_pair(xx, torch.from_numpy(w1).to(dev), torch.from_numpy(w2).to(dev), out1, out2, eps, torch.from_numpy(kernel).to(dev),
+                          tail if taps > 1 else tail[:, :0], row_slot)
+        else:
+            ops.norm_pair(xx, torch.from_numpy(w1).to(dev), torch.from_numpy(w2).to(dev), out1, out2, eps)
+        got1.append(out1[:3].float().cpu().numpy())
+        got2.append(out2[:3].float().cpu().numpy())
+    got1, got2 = np.stack(got1), np.stack(got2)
+    for i in range(3):
+        h = pf.rms_norm(pf.f64(xs[:, i]), w1, eps)
+        if dtype == "bfloat16":
+            h = pf.f64(pf.bf16_round(h))                            # the convolution reads the rounded norm
+        close(got1[:, i], pf.short_conv_residual(h, pf.f64(kernel)) if taps else h, dtype, f"sequence {i}, first output")
+        close(got2[:, i], pf.rms_norm(pf.f64(xs[:, i]), w2, eps), dtype, f"sequence {i}, second output")
+    assert float(tail[2].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_polynorm(dtype):
     from borrowed_compute_b200 import ops
 
@@ -263,6 +300,23 @@ def test_unequal_batch_against_each_alone(dtype):
     for i in range(4):
         close(np.concatenate(got[i]), refs[i], dtype, f"sequence {i}")
     assert eng.cache.slots.live() == []
+
+
+def test_single_rows_in_one_launch_or_three_give_the_same_bits():
+    """Steps of single rows run the delta rule as one launch; the three kernels of a prompt step must give the
+    same bits, and so must a prompt cut anywhere (float32: every sum's order depends on the row alone)."""
+    from borrowed_compute_b200.parts import delta_rule
+
+    eng, cfg, w = small("Q", "float32")
+    toks = tokens_for(77, 90, cfg["vocab"])
+    one = run_cut(eng, toks, [40])
+    graphs, eng.use_graphs, delta_rule.split_steps = eng.use_graphs, False, True
+    try:
+        three = run_cut(eng, toks, [40])
+    finally:
+        eng.use_graphs, delta_rule.split_steps = graphs, False
+    assert np.array_equal(one, three)
+    assert np.array_equal(one, run_cut(eng, toks, [7, 2, 60, 1, 1, 19]))
 
 
 def test_slots_and_pages_used_again():
