@@ -6,7 +6,7 @@
 #include "common.cuh"
 
 template <class T>
-__global__ void __launch_bounds__(256) polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, T* __restrict__ out, int F,
+__global__ void __launch_bounds__(1024) polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, T* __restrict__ out, int F,
                                                        float eps) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -15,11 +15,26 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const float* __restrict__
     const float* zr = z + (size_t)blockIdx.x * F;
     T* o = out + (size_t)blockIdx.x * F;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float v = zr[i], v2 = v * v;
-        s1 += v2;
-        s2 = fmaf(v2, v2, s2);
-        s3 = fmaf(v2 * v, v2 * v, s3);
+    // A thread's share is taken in ascending order, four at a time where rows are 16-byte aligned.
+    if (F % 4 == 0) {
+        for (int i = 4 * threadIdx.x; i < F; i += 4 * blockDim.x) {
+            const float4 q = *reinterpret_cast<const float4*>(zr + i);
+            const float e4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float v = e4[k], v2 = v * v;
+                s1 += v2;
+                s2 = fmaf(v2, v2, s2);
+                s3 = fmaf(v2 * v, v2 * v, s3);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < F; i += blockDim.x) {
+            const float v = zr[i], v2 = v * v;
+            s1 += v2;
+            s2 = fmaf(v2, v2, s2);
+            s3 = fmaf(v2 * v, v2 * v, s3);
+        }
     }
     s1 = block_sum(s1, scratch);
     s2 = block_sum(s2, scratch);
@@ -34,7 +49,9 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const float* __restrict__
 template <class T> static int launch(const float* z, const float* coef, void* out, int rows, int F, float eps, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && F > 0, "polynorm: bad sizes rows=%d F=%d", rows, F);
     if (rows == 0) return BC_OK;
-    bc_launch(polynorm_kernel<T>, dim3(rows), dim3(256), 0, s, z, coef, (T*)out, F, eps);
+    // The block's size depends on the row's width alone, never on the number of rows: a row's sums are the same bits in any batch.
+    const int threads = F >= 8192 ? 1024 : F >= 2048 ? 512 : 256;
+    bc_launch(polynorm_kernel<T>, dim3(rows), dim3(threads), 0, s, z, coef, (T*)out, F, eps);
     BC_LAUNCH_STATUS();
 }
 // z: [rows, F] float; coef: the four numbers a, b, c, e; out: [rows, F].

@@ -11,7 +11,7 @@
 #include "common.cuh"
 
 template <class T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qkv_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ q_weight,
                    const float* __restrict__ k_weight, const float* __restrict__ cos_sin, int n_positions, const int* __restrict__ row_pos,
                    const int* __restrict__ row_slot, const int* __restrict__ page_table, int max_pages, int n_pages, T* __restrict__ q_out,
@@ -82,7 +82,10 @@ static int launch(const float* qkv, const float* bias, const float* q_weight, co
     BC_CHECK_ARG(rot >= 0 && rot % 2 == 0 && rot <= D, "qkv_prepare: %d rotated dimensions of a head of %d", rot, D);
     BC_CHECK_ARG(!normed || (q_weight && k_weight), "qkv_prepare: the norm needs its weights");
     if (rows == 0) return BC_OK;
-    bc_launch(qkv_prepare_kernel<T>, dim3(rows), dim3(256), 0, s, qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot,
+    // The block's size depends on the row's width alone, never on the number of rows: a row's sums are the same bits in any batch.
+    const int width = H * D + G * D;
+    const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
+    bc_launch(qkv_prepare_kernel<T>, dim3(rows), dim3(threads), 0, s, qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot,
               page_table, max_pages, n_pages, (T*)q_out, (T*)k_cache, (T*)v_cache, H, G, D, DV, rot, eps, normed, write_cache);
     BC_LAUNCH_STATUS();
 }

@@ -1,5 +1,5 @@
 // A short causal convolution over time on every channel, added to its own input:
-//   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - (taps - 1 - j), c]
+//   out[t, c] = h[t, c] + sum_{j < taps} w[j, c] * h[t - (taps - 1 - j), c]
 // with zeros before a sequence's first position.  The last taps - 1 inputs of a sequence
 // are state that outlives the step: tail[slot][i][c] holds the input at position
 // start - (taps - 1) + i, where `start` is how many positions the slot held before this
@@ -16,32 +16,81 @@
 
 #define SC_THREADS 256
 
-template <class T>
+// V values of the activation type, as floats and back: one 16-byte access where V * sizeof(T) is 16.
+template <class T, int V> __device__ __forceinline__ void load_values(const T* p, float* v) {
+    if constexpr (V == 1) {
+        v[0] = to_f32(p[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+        const uint4 q = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+template <class T, int V> __device__ __forceinline__ void store_values(T* p, const float* v) {
+    if constexpr (V == 1) {
+        p[0] = from_f32<T>(v[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// A thread takes V neighbouring channels of one row (V = 16 bytes' worth where the width allows, else 1).
+template <class T, int V>
 __global__ void __launch_bounds__(SC_THREADS)
 short_conv_kernel(const T* __restrict__ h, const float* __restrict__ w, T* __restrict__ tail, const int* __restrict__ seq_rows,
                   const int* __restrict__ seq_slot, T* __restrict__ out, int E, int taps, int n_slots, int update_tail) {
     pdl_launch_dependents();
     pdl_wait();
     const int tok = blockIdx.x, sq = blockIdx.y;
-    const int c = blockIdx.z * SC_THREADS + threadIdx.x;
+    const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
     const int slot = seq_slot[sq];
     const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
     if (slot < 0 || slot >= n_slots || tok >= n_new || c >= E) return;
     T* tl = tail + (size_t)slot * (taps - 1) * E + c;
     const T* hr = h + (size_t)row0 * E + c;
-    const float own = to_f32(hr[(size_t)tok * E]);
-    float acc = 0.0f;
+    float own[V], acc[V], v[V];
+    load_values<T, V>(hr + (size_t)tok * E, own);
+#pragma unroll
+    for (int k = 0; k < V; k++) acc[k] = 0.0f;
     for (int j = 0; j < taps; j++) {
         const int back = taps - 1 - j;
         // The input `back` positions earlier: a row of this step, or one the tail kept.
-        const float v = back == 0 ? own : back <= tok ? to_f32(hr[(size_t)(tok - back) * E]) : to_f32(tl[(size_t)(tok - back + taps - 1) * E]);
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+        if (back == 0) {
+#pragma unroll
+            for (int k = 0; k < V; k++) v[k] = own[k];
+        } else if (back <= tok) {
+            load_values<T, V>(hr + (size_t)(tok - back) * E, v);
+        } else {
+            load_values<T, V>(tl + (size_t)(tok - back + taps - 1) * E, v);
+        }
+#pragma unroll
+        for (int k = 0; k < V; k++) acc[k] = fmaf(w[(size_t)j * E + c + k], v[k], acc[k]);
     }
-    out[(size_t)(row0 + tok) * E + c] = from_f32<T>(own + acc);
+#pragma unroll
+    for (int k = 0; k < V; k++) acc[k] += own[k];
+    store_values<T, V>(out + (size_t)(row0 + tok) * E + c, acc);
     if (update_tail) {
         // One row a sequence: the tail moves up by one and takes this row's input.
-        for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
-        if (taps > 1) tl[(size_t)(taps - 2) * E] = from_f32<T>(own);
+        for (int i = 0; i + 2 < taps; i++) {
+            load_values<T, V>(tl + (size_t)(i + 1) * E, v);
+            store_values<T, V>(tl + (size_t)i * E, v);
+        }
+        if (taps > 1) store_values<T, V>(tl + (size_t)(taps - 2) * E, own);
     }
 }
 
@@ -71,7 +120,7 @@ short_conv_tail_kernel(const T* __restrict__ h, T* __restrict__ tail, const int*
 // row a sequence only (row r is sequence r's one row): the sum runs over the tail and the row's own rounded
 // value in the same order as in short_conv_kernel, so both ways give the same bits; the tail moves up by one.
 template <class T>
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(1024)
 norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ w2, const float* __restrict__ cw,
                       T* __restrict__ tail, const int* __restrict__ row_slot, T* __restrict__ out1, T* __restrict__ out2, int E, float eps,
                       int taps, int n_slots, int update_tail) {
@@ -97,8 +146,8 @@ norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1,
         T* tl = tail + (size_t)slot * (taps - 1) * E + c;
         const float own = to_f32(h);
         float acc = 0.0f;
-        for (int j = 0; j + 1 < taps; j++) acc = fmaf(cw[(size_t)c * taps + j], to_f32(tl[(size_t)j * E]), acc);
-        acc = fmaf(cw[(size_t)c * taps + taps - 1], own, acc);
+        for (int j = 0; j + 1 < taps; j++) acc = fmaf(cw[(size_t)j * E + c], to_f32(tl[(size_t)j * E]), acc);
+        acc = fmaf(cw[(size_t)(taps - 1) * E + c], own, acc);
         out1[(size_t)r * E + c] = from_f32<T>(own + acc);
         if (update_tail) {
             for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
@@ -113,13 +162,15 @@ static int launch_pair(const float* x, const float* w1, const float* w2, const f
     BC_CHECK_ARG(rows >= 0 && E > 0 && taps >= 0, "norm_pair: bad sizes rows=%d E=%d taps=%d", rows, E, taps);
     BC_CHECK_ARG(taps == 0 || (cw && row_slot && (tail || taps == 1)), "norm_pair: the convolution needs its weights, the rows' slots and the tail");
     if (rows == 0) return BC_OK;
-    bc_launch(norm_pair_conv_kernel<T>, dim3(rows), dim3(SC_THREADS), 0, s, x, w1, w2, cw, (T*)tail, row_slot, (T*)out1, (T*)out2, E, eps, taps,
+    // The block's size depends on the row's width alone, never on the number of rows: a row's statistic is the same bits in any batch.
+    const int threads = E >= 4096 ? 1024 : E >= 1024 ? 512 : 256;
+    bc_launch(norm_pair_conv_kernel<T>, dim3(rows), dim3(threads), 0, s, x, w1, w2, cw, (T*)tail, row_slot, (T*)out1, (T*)out2, E, eps, taps,
               n_slots, update_tail);
     BC_LAUNCH_STATUS();
 }
 
 // x: [rows, E] float; w1, w2: [E] float; out1, out2: [rows, E] (out2 and w2 may be null).  taps 0: no convolution;
-// else cw [E, taps], tail [n_slots, taps - 1, E], row_slot [rows], every row being its sequence's only row of the step.
+// else cw [taps, E], tail [n_slots, taps - 1, E], row_slot [rows], every row being its sequence's only row of the step.
 extern "C" int bc_norm_pair_f32(const float* x, const float* w1, const float* w2, const float* cw, void* tail, const int* row_slot, void* out1,
                                 void* out2, int rows, int E, float eps, int taps, int n_slots, int update_tail, cudaStream_t s) {
     return launch_pair<float>(x, w1, w2, cw, tail, row_slot, out1, out2, rows, E, eps, taps, n_slots, update_tail, s);
@@ -138,8 +189,14 @@ static int launch(const void* h, const float* w, void* tail, const int* seq_rows
     if (seqs == 0 || max_new == 0) return BC_OK;
     const int chunks = (E + SC_THREADS - 1) / SC_THREADS;
     const int fused = write_tail && max_new == 1;
-    bc_launch(short_conv_kernel<T>, dim3(max_new, seqs, chunks), dim3(SC_THREADS), 0, s, (const T*)h, w, (T*)tail, seq_rows, seq_slot, (T*)out,
-              E, taps, n_slots, fused);
+    constexpr int V = 16 / (int)sizeof(T);
+    const bool wide = E % V == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)tail % 16 == 0;
+    if (wide)
+        bc_launch(short_conv_kernel<T, V>, dim3(max_new, seqs, (E / V + SC_THREADS - 1) / SC_THREADS), dim3(SC_THREADS), 0, s, (const T*)h, w,
+                  (T*)tail, seq_rows, seq_slot, (T*)out, E, taps, n_slots, fused);
+    else
+        bc_launch(short_conv_kernel<T, 1>, dim3(max_new, seqs, chunks), dim3(SC_THREADS), 0, s, (const T*)h, w, (T*)tail, seq_rows, seq_slot,
+                  (T*)out, E, taps, n_slots, fused);
     if (write_tail && !fused && taps > 1) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {
@@ -152,7 +209,7 @@ static int launch(const void* h, const float* w, void* tail, const int* seq_rows
     BC_LAUNCH_STATUS();
 }
 
-// h, out: [rows, E]; w: [E, taps] float; tail: [n_slots, taps - 1, E].  Sequence s owns rows
+// h, out: [rows, E]; w: [taps, E] float (tap by tap, so that neighbouring channels are neighbours); tail: [n_slots, taps - 1, E].  Sequence s owns rows
 // seq_rows[s] .. seq_rows[s + 1] and lives in slot seq_slot[s] (negative: skipped, its rows of
 // `out` are left untouched).  max_new: the most rows any sequence brings.  write_tail 0 leaves
 // the tail as it was (a run that reads another run's memory).

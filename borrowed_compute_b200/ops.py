@@ -541,24 +541,24 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
 
 # ------------------------------------------------------- parts of other mixers and feed-forwards
 
-def short_conv(h: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
+def short_conv(h: torch.Tensor, weight_t: torch.Tensor, tail: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
                out: torch.Tensor, seqs: int, max_new: int, write_tail: bool = True) -> None:
-    """out = h + causal convolution of h over time on every channel; ``weight`` [E, taps] float32,
-    ``tail`` [slots, taps - 1, E] holds every slot's last inputs and is brought up to date."""
+    """out = h + causal convolution of h over time on every channel; ``weight_t`` [taps, E] float32 (the kernel
+    transposed: tap by tap), ``tail`` [slots, taps - 1, E] holds every slot's last inputs and is brought up to date."""
     _need(h, "h")
-    _need(weight, "weight", torch.float32)
+    _need(weight_t, "weight_t", torch.float32)
     _need(tail, "tail", h.dtype)
     _need(seq_rows, "seq_rows", torch.int32)
     _need(seq_slot, "seq_slot", torch.int32)
     _need(out, "out", h.dtype)
-    E, taps = weight.shape
+    taps, E = weight_t.shape
     if h.shape[-1] != E or out.shape != h.shape or tuple(tail.shape[1:]) != (taps - 1, E):
-        raise KernelError(f"short_conv: h {tuple(h.shape)}, out {tuple(out.shape)}, tail {tuple(tail.shape)} do not fit weight {(E, taps)}")
+        raise KernelError(f"short_conv: h {tuple(h.shape)}, out {tuple(out.shape)}, tail {tuple(tail.shape)} do not fit weight {(taps, E)}")
     if h.data_ptr() == out.data_ptr():
         raise KernelError("short_conv: out must not be h (rows read their predecessors)")
     _bounds("short_conv: seq_slot", seq_slot, tail.shape[0], seqs, lowest=-1)
     _bounds("short_conv: seq_rows", seq_rows, h.shape[0] + 1, seqs + 1)
-    _call(_fn("bc_short_conv_" + _suffix(h.dtype)), _ptr(h), _ptr(weight), _ptr(tail), _ptr(seq_rows), _ptr(seq_slot), _ptr(out),
+    _call(_fn("bc_short_conv_" + _suffix(h.dtype)), _ptr(h), _ptr(weight_t), _ptr(tail), _ptr(seq_rows), _ptr(seq_slot), _ptr(out),
           _c_int(seqs), _c_int(max_new), _c_int(E), _c_int(taps), _c_int(tail.shape[0]), _c_int(1 if write_tail else 0), _stream())
 
 
@@ -566,7 +566,7 @@ def norm_pair(x: torch.Tensor, w1: torch.Tensor, w2: Optional[torch.Tensor], out
               conv_weight: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None, row_slot: Optional[torch.Tensor] = None,
               write_tail: bool = True) -> None:
     """Two RMS norms of the same rows with one statistic: out1 = x / rms(x) * w1, out2 = x / rms(x) * w2 (the second
-    may be left out).  With ``conv_weight`` [E, taps] the first output also passes the short causal convolution of
+    may be left out).  With ``conv_weight`` [taps, E] (transposed, as for ``short_conv``) the first output also passes the short causal convolution of
     ``short_conv``, for steps in which every sequence brings one row (row r belongs to slot ``row_slot[r]``); the
     tail is brought up to date."""
     _need(x, "x", torch.float32)
@@ -587,29 +587,30 @@ def norm_pair(x: torch.Tensor, w1: torch.Tensor, w2: Optional[torch.Tensor], out
         _need(conv_weight, "conv_weight", torch.float32)
         _need(tail, "tail", out1.dtype)
         _need(row_slot, "row_slot", torch.int32)
-        taps, n_slots = conv_weight.shape[1], tail.shape[0]
-        if conv_weight.shape[0] != E or tuple(tail.shape[1:]) != (taps - 1, E) or row_slot.numel() < rows:
+        taps, n_slots = conv_weight.shape[0], tail.shape[0]
+        if conv_weight.shape[1] != E or tuple(tail.shape[1:]) != (taps - 1, E) or row_slot.numel() < rows:
             raise KernelError(f"norm_pair: conv weight {tuple(conv_weight.shape)}, tail {tuple(tail.shape)} do not fit {E} channels")
         _bounds("norm_pair: row_slot", row_slot, n_slots, rows, lowest=-1)
     _call(_fn("bc_norm_pair_" + _suffix(out1.dtype)), _ptr(x), _ptr(w1), _ptr(w2), _ptr(conv_weight), _ptr(tail), _ptr(row_slot), _ptr(out1),
           _ptr(out2), _c_int(rows), _c_int(E), _c_float(eps), _c_int(taps), _c_int(n_slots), _c_int(1 if write_tail else 0), _stream())
 
 
-def delta_prepare(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, decay: torch.Tensor, unit: torch.Tensor,
+def delta_prepare(proj: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, decay: torch.Tensor, unit: torch.Tensor,
                   removal: torch.Tensor, dots: torch.Tensor, heads: int, head_dim: int, decay_scale: float, key_eps: float) -> None:
     """From the fused projection [rows, 5 H D + inner] (r, k, v, gate, a, decay's inner projection; float32): per key
     channel the decay exp(-decay_scale * sigmoid(w2 tanh(inner) + w0)), the key over its length, the removal
-    rate sigmoid(a + a_bias) times that unit key, and per head the dot products r.(removal) and r.k."""
+    rate sigmoid(a + a_bias) times that unit key, and per head the dot products r.(removal) and r.k.
+    ``w2t`` is w2 transposed, [inner, H D]."""
     rows, stride = proj.shape
     HD = heads * head_dim
-    inner = w2.shape[1]
-    for t, name in ((proj, "proj"), (w2, "w2"), (w0, "w0"), (a_bias, "a_bias"), (decay, "decay"), (unit, "unit"), (removal, "removal"), (dots, "dots")):
+    inner = w2t.shape[0]
+    for t, name in ((proj, "proj"), (w2t, "w2t"), (w0, "w0"), (a_bias, "a_bias"), (decay, "decay"), (unit, "unit"), (removal, "removal"), (dots, "dots")):
         _need(t, name, torch.float32)
-    if w2.shape[0] != HD or w0.numel() != HD or a_bias.numel() != HD or stride != 5 * HD + inner:
-        raise KernelError(f"delta_prepare: proj {tuple(proj.shape)}, w2 {tuple(w2.shape)} do not fit {heads} heads of {head_dim}")
+    if w2t.shape[1] != HD or w0.numel() != HD or a_bias.numel() != HD or stride != 5 * HD + inner:
+        raise KernelError(f"delta_prepare: proj {tuple(proj.shape)}, w2t {tuple(w2t.shape)} do not fit {heads} heads of {head_dim}")
     if any(tuple(t.shape) != (rows, HD) for t in (decay, unit, removal)) or tuple(dots.shape) != (rows, heads, 2):
         raise KernelError("delta_prepare: outputs must be [rows, H D] and dots [rows, H, 2]")
-    _call(_fn("bc_delta_prepare"), _ptr(proj), _c_int(stride), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(decay), _ptr(unit), _ptr(removal),
+    _call(_fn("bc_delta_prepare"), _ptr(proj), _c_int(stride), _ptr(w2t), _ptr(w0), _ptr(a_bias), _ptr(decay), _ptr(unit), _ptr(removal),
           _ptr(dots), _c_int(rows), _c_int(heads), _c_int(head_dim), _c_int(inner), _c_float(decay_scale), _c_float(key_eps), _stream())
 
 
@@ -651,23 +652,23 @@ def delta_step_accepts(head_dim: int) -> bool:
     return 0 < head_dim <= 128
 
 
-def delta_step(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor,
+def delta_step(proj: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor,
                row_slot: torch.Tensor, out: torch.Tensor, heads: int, head_dim: int, decay_scale: float, key_eps: float, norm_eps: float,
                write_state: bool = True) -> None:
     """``delta_prepare``, one step of ``delta_scan`` and ``delta_finish`` in one launch, for steps in which every
     sequence brings one row (row r lives in slot ``row_slot[r]``); the same bits as the three."""
-    for t, name in ((proj, "proj"), (w2, "w2"), (w0, "w0"), (a_bias, "a_bias"), (norm_weight, "norm_weight"), (state, "state")):
+    for t, name in ((proj, "proj"), (w2t, "w2t"), (w0, "w0"), (a_bias, "a_bias"), (norm_weight, "norm_weight"), (state, "state")):
         _need(t, name, torch.float32)
     _need(row_slot, "row_slot", torch.int32)
     _need(out, "out")
     rows, stride = proj.shape
-    HD, inner = heads * head_dim, w2.shape[1]
-    if w2.shape[0] != HD or w0.numel() != HD or a_bias.numel() != HD or norm_weight.numel() != HD or stride != 5 * HD + inner:
-        raise KernelError(f"delta_step: proj {tuple(proj.shape)}, w2 {tuple(w2.shape)} do not fit {heads} heads of {head_dim}")
+    HD, inner = heads * head_dim, w2t.shape[0]
+    if w2t.shape[1] != HD or w0.numel() != HD or a_bias.numel() != HD or norm_weight.numel() != HD or stride != 5 * HD + inner:
+        raise KernelError(f"delta_step: proj {tuple(proj.shape)}, w2t {tuple(w2t.shape)} do not fit {heads} heads of {head_dim}")
     if tuple(state.shape[1:]) != (heads, head_dim, head_dim) or tuple(out.shape) != (rows, HD) or row_slot.numel() < rows:
         raise KernelError(f"delta_step: state {tuple(state.shape)} or out {tuple(out.shape)} do not fit")
     _bounds("delta_step: row_slot", row_slot, state.shape[0], rows, lowest=-1)
-    _call(_fn("bc_delta_step_" + _suffix(out.dtype)), _ptr(proj), _c_int(stride), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(norm_weight),
+    _call(_fn("bc_delta_step_" + _suffix(out.dtype)), _ptr(proj), _c_int(stride), _ptr(w2t), _ptr(w0), _ptr(a_bias), _ptr(norm_weight),
           _ptr(state), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(head_dim), _c_int(inner), _c_float(decay_scale),
           _c_float(key_eps), _c_float(norm_eps), _c_int(state.shape[0]), _c_int(1 if write_state else 0), _stream())
 

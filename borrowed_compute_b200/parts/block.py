@@ -61,7 +61,7 @@ class ParallelBlock(Block):
             if conv is not None and tail is None:
                 raise RuntimeError("the convolution was given no state: the cache does not serve this block")
             ops.norm_pair(residual, self.norm1.weight, None if h2 is None else self.norm2.weight, h, h2, self.norm1.eps,
-                          None if conv is None else conv.weight, None if conv is None else (tail if conv.taps > 1 else tail[:, :0]),
+                          None if conv is None else conv.weight_t, None if conv is None else (tail if conv.taps > 1 else tail[:, :0]),
                           ctx.row_slot, write_tail=mem.writes)
             done = conv is not None
         else:

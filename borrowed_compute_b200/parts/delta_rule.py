@@ -59,7 +59,8 @@ class GeneralizedDelta(Mixer):
         # One product for all that is read from h: r, k, v, the gate, the removal rate, the decay's inner projection.
         self.w_in = torch.cat([tensors[n] for n in ("r", "k", "v", "g", "a", "w1")], dim=0).contiguous()
         self.w_o = tensors["o"].contiguous()
-        self.a_bias, self.w2, self.w0, self.norm_weight = (tensors[n].contiguous() for n in ("a.b", "w2", "w0", "norm"))
+        self.a_bias, self.w0, self.norm_weight = (tensors[n].contiguous() for n in ("a.b", "w0", "norm"))
+        self.w2_t = tensors["w2"].t().contiguous()      # [rank, heads * dim]: the threads of a head read neighbouring values
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         if mem.state is None:
@@ -71,13 +72,13 @@ class GeneralizedDelta(Mixer):
         y = torch.empty((rows, hd), dtype=x.dtype, device=dev)
         if ctx.decode and not split_steps and ops.delta_step_accepts(D):
             # One row a sequence: the three kernels below as one launch (the same bits).
-            ops.delta_step(proj, self.w2, self.w0, self.a_bias, self.norm_weight, mem.state, ctx.row_slot, y, H, D, self.decay_scale,
+            ops.delta_step(proj, self.w2_t, self.w0, self.a_bias, self.norm_weight, mem.state, ctx.row_slot, y, H, D, self.decay_scale,
                            self.key_eps, self.norm_eps, write_state=mem.writes)
             products.linear(y, self.w_o, residual, products.EPI_ADD_F32, "output product")
             return
         decay, unit, removal = (torch.empty((rows, hd), dtype=f32, device=dev) for _ in range(3))
         dots = torch.empty((rows, H, 2), dtype=f32, device=dev)
-        ops.delta_prepare(proj, self.w2, self.w0, self.a_bias, decay, unit, removal, dots, H, D, self.decay_scale, self.key_eps)
+        ops.delta_prepare(proj, self.w2_t, self.w0, self.a_bias, decay, unit, removal, dots, H, D, self.decay_scale, self.key_eps)
         o = torch.empty((rows, hd), dtype=f32, device=dev)
         ops.delta_scan(proj, decay, unit, removal, dots, mem.state, ctx.seq_rows, ctx.seq_slot, o, ctx.seqs, H, D, write_state=mem.writes)
         ops.delta_finish(o, proj, 3 * hd, self.norm_weight, y, H, D, self.norm_eps)

@@ -29,7 +29,7 @@ class CausalConvResidual(ShortConvolution):
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
-        self.weight = tensors[self.tensor].contiguous()
+        self.weight_t = tensors[self.tensor].t().contiguous()      # [taps, width]: neighbouring channels are neighbours in memory
 
     def state_need(self) -> Optional[StateNeed]:
         # One row more than needed when taps is 1, so that the tensor is never empty.
@@ -39,4 +39,4 @@ class CausalConvResidual(ShortConvolution):
         if state is None:
             raise RuntimeError("the convolution was given no state: the cache does not serve this block")
         tail = state if self.taps > 1 else state[:, :0]
-        ops.short_conv(h, self.weight, tail, ctx.seq_rows, ctx.seq_slot, out, ctx.seqs, ctx.max_new, write_tail=writes)
+        ops.short_conv(h, self.weight_t, tail, ctx.seq_rows, ctx.seq_slot, out, ctx.seqs, ctx.max_new, write_tail=writes)

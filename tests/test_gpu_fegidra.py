@@ -122,7 +122,7 @@ def test_short_convolution_whole_and_in_portions(dtype, taps):
         seq_slot = torch.tensor([slots[i] for i in live] + [-1], dtype=torch.int32, device=dev)[:len(live)]
         out = torch.zeros_like(h)
         t = tail if taps > 1 else tail[:, :0]
-        ops.short_conv(h, torch.from_numpy(kernel).to(dev), t, seq_rows, seq_slot, out, len(live), max(portion[i] for i in live))
+        ops.short_conv(h, torch.from_numpy(np.ascontiguousarray(kernel.T)).to(dev), t, seq_rows, seq_slot, out, len(live), max(portion[i] for i in live))
         o = out.float().cpu().numpy()
         at = 0
         for i in live:
@@ -154,7 +154,7 @@ def test_two_norms_with_one_statistic_and_the_convolution_riding_along(dtype, ta
         xx = torch.cat([x, torch.ones((1, E), device=dev)])          # a padding row (slot -1) after the three
         row_slot = torch.tensor(slots + [-1], dtype=torch.int32, device=dev)
         if taps:
-            ops.norm_pair(xx, torch.from_numpy(w1).to(dev), torch.from_numpy(w2).to(dev), out1, out2, eps, torch.from_numpy(kernel).to(dev),
+            ops.norm_pair(xx, torch.from_numpy(w1).to(dev), torch.from_numpy(w2).to(dev), out1, out2, eps, torch.from_numpy(np.ascontiguousarray(kernel.T)).to(dev),
                           tail if taps > 1 else tail[:, :0], row_slot)
         else:
             ops.norm_pair(xx, torch.from_numpy(w1).to(dev), torch.from_numpy(w2).to(dev), out1, out2, eps)
@@ -223,7 +223,7 @@ def test_delta_rule_kernels(heads, dim, rank):
             seq_slot = torch.tensor([slots[i] for i in live] + [-1], dtype=torch.int32, device=dev)       # the last one is padding
             decay, unit, removal, o = (torch.empty((rows, HD), dtype=f32, device=dev) for _ in range(4))
             dots = torch.empty((rows, heads, 2), dtype=f32, device=dev)
-            ops.delta_prepare(p, torch.from_numpy(w2).to(dev), torch.from_numpy(w0).to(dev), torch.from_numpy(a_b).to(dev), decay, unit,
+            ops.delta_prepare(p, torch.from_numpy(np.ascontiguousarray(w2.T)).to(dev), torch.from_numpy(w0).to(dev), torch.from_numpy(a_b).to(dev), decay, unit,
                               removal, dots, heads, dim, pf.DECAY_SCALE, pf.KEY_EPS)
             ops.delta_scan(p, decay, unit, removal, dots, state, seq_rows, seq_slot, o, len(live) + 1, heads, dim)
             y = torch.empty((rows, HD), dtype=f32, device=dev)
