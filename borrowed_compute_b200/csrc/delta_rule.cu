@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(64 * R)
 delta_step_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ w2t, const float* __restrict__ w0,
                   const float* __restrict__ a_bias, const float* __restrict__ norm_w, float* __restrict__ state,
                   const int* __restrict__ row_slot, T* __restrict__ out, int H, int D, int inner, float decay_scale, float key_eps,
-                  float norm_eps, int n_slots, int write_state) {
+                  float norm_eps, int n_slots, int write_state, int slab_in_shared) {
     constexpr int DP = DR_LANES * R;
     extern __shared__ __align__(16) float sm[];
     __shared__ float scratch[32];
@@ -307,6 +307,11 @@ delta_step_kernel(const float* __restrict__ proj, int stride, const float* __res
     if (slot < 0 || slot >= n_slots) return;
     const float* p = proj + (size_t)row * stride;
     for (int j = threadIdx.x; j < inner; j += blockDim.x) th[j] = tanhf(p[5 * HD + j]);
+    // The head's slab of the decay matrix, [inner][D], fetched by all threads at once where it fits: the D threads
+    // that add it up (in the same order as ever) then read shared memory instead of waiting for one load a term.
+    float* slab = so + ((D + 3) & ~3);
+    if (slab_in_shared)
+        for (int e = threadIdx.x; e < inner * D; e += blockDim.x) slab[e] = w2t[(size_t)(e / D) * HD + head * D + e % D];
     __syncthreads();
     const int d = threadIdx.x, c = head * D + d;
     const bool mine = d < D;
@@ -316,8 +321,13 @@ delta_step_kernel(const float* __restrict__ proj, int stride, const float* __res
         k = p[HD + c];
         a = sigmoid_f(p[4 * HD + c] + a_bias[c]);
         float z = 0.0f;
+        if (slab_in_shared) {
 #pragma unroll 8
-        for (int j = 0; j < inner; j++) z = fmaf(w2t[(size_t)j * HD + c], th[j], z);
+            for (int j = 0; j < inner; j++) z = fmaf(slab[j * D + d], th[j], z);
+        } else {
+#pragma unroll 8
+            for (int j = 0; j < inner; j++) z = fmaf(w2t[(size_t)j * HD + c], th[j], z);
+        }
         w = expf(-decay_scale * sigmoid_f(z + w0[c]));
     }
     const float kk = block_sum(k * k, scratch);
@@ -378,9 +388,13 @@ static int step(const float* proj, int stride, const float* w2t, const float* w0
     if (rows == 0) return BC_OK;
     const int threads = DR_LANES * ((D + 3) / 4 * 4);
     const dim3 grid(rows, H);
-#define DS_CASE(R)                                                                                                                         \
-    bc_launch(delta_step_kernel<R, T>, grid, dim3(threads), (size_t)(((inner + 3) & ~3) + 5 * DR_LANES * R + D) * sizeof(float), s, proj, \
-              stride, w2t, w0, a_bias, norm_w, state, row_slot, (T*)out, H, D, inner, decay_scale, key_eps, norm_eps, n_slots, write_state)
+    const size_t slab = (size_t)inner * D * sizeof(float);
+    const int slab_in_shared = slab <= 32 * 1024;
+#define DS_CASE(R)                                                                                                                      \
+    bc_launch(delta_step_kernel<R, T>, grid, dim3(threads),                                                                             \
+              (size_t)(((inner + 3) & ~3) + 5 * DR_LANES * R + ((D + 3) & ~3)) * sizeof(float) + (slab_in_shared ? slab : 0), s, proj, \
+              stride, w2t, w0, a_bias, norm_w, state, row_slot, (T*)out, H, D, inner, decay_scale, key_eps, norm_eps, n_slots,          \
+              write_state, slab_in_shared)
     if (D <= 16) DS_CASE(2);
     else if (D <= 32) DS_CASE(4);
     else if (D <= 64) DS_CASE(8);

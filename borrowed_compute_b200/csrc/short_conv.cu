@@ -39,13 +39,15 @@ template <class T, int V> __device__ __forceinline__ void store_values(T* p, con
     } else if constexpr (sizeof(T) == 4) {
         *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
-        uint32_t w[4];
+        static_assert(sizeof(T) == 4 || V == 1 || V == 4 || V == 8, "bf16 values go four or eight at a time");
+        uint32_t w[V / 2];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
+        for (int i = 0; i < V / 2; i++) {
             __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+        if constexpr (V == 8) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+        else *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
     }
 }
 
@@ -94,6 +96,53 @@ short_conv_kernel(const T* __restrict__ h, const float* __restrict__ w, T* __res
     }
 }
 
+// The same sums for prompts: a thread walks SC_ROWS rows of one sequence for its V channels with the last
+// TAPS - 1 inputs and the kernel in registers, so that every input is read once.
+#define SC_ROWS 8
+template <class T, int V, int TAPS>
+__global__ void __launch_bounds__(SC_THREADS)
+short_conv_rows_kernel(const T* __restrict__ h, const float* __restrict__ w, const T* __restrict__ tail, const int* __restrict__ seq_rows,
+                       const int* __restrict__ seq_slot, T* __restrict__ out, int E, int n_slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tok0 = blockIdx.x * SC_ROWS, sq = blockIdx.y;
+    const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
+    const int slot = seq_slot[sq];
+    const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
+    if (slot < 0 || slot >= n_slots || tok0 >= n_new || c >= E) return;
+    const T* tl = tail + (size_t)slot * (TAPS - 1) * E + c;
+    const T* hr = h + (size_t)row0 * E + c;
+    float wt[TAPS][V], win[TAPS - 1][V], own[V], acc[V];
+#pragma unroll
+    for (int j = 0; j < TAPS; j++)
+#pragma unroll
+        for (int k = 0; k < V; k++) wt[j][k] = w[(size_t)j * E + c + k];
+#pragma unroll
+    for (int i = 0; i < TAPS - 1; i++) {       // the input at row tok0 - (TAPS - 1) + i of the step, or what the tail kept of it
+        const int rel = tok0 - (TAPS - 1) + i;
+        if (rel >= 0) load_values<T, V>(hr + (size_t)rel * E, win[i]);
+        else load_values<T, V>(tl + (size_t)(rel + TAPS - 1) * E, win[i]);
+    }
+    const int n = min(SC_ROWS, n_new - tok0);
+    for (int t = 0; t < n; t++) {
+        load_values<T, V>(hr + (size_t)(tok0 + t) * E, own);
+#pragma unroll
+        for (int k = 0; k < V; k++) {
+            float a = 0.0f;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; j++) a = fmaf(wt[j][k], win[j][k], a);
+            acc[k] = own[k] + fmaf(wt[TAPS - 1][k], own[k], a);
+        }
+        store_values<T, V>(out + (size_t)(row0 + tok0 + t) * E + c, acc);
+#pragma unroll
+        for (int i = 0; i + 1 < TAPS - 1; i++)
+#pragma unroll
+            for (int k = 0; k < V; k++) win[i][k] = win[i + 1][k];
+#pragma unroll
+        for (int k = 0; k < V; k++) win[TAPS - 2][k] = own[k];
+    }
+}
+
 // The tail after the step: the inputs at the last taps - 1 positions the sequence now holds,
 // from this step's rows where they reach that far back, else from the old tail (entry i takes
 // old entry i + n_new, which lies above it, so ascending i never reads what it has written).
@@ -129,29 +178,58 @@ norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1,
     pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)r * E;
+    // A thread takes four neighbouring channels at a time where the width allows (W = 4), else one: which values it
+    // adds up and in which order depends on the width alone.
+    const int W = E % 4 == 0 ? 4 : 1;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < E; c += blockDim.x) ss += xr[c] * xr[c];
+    if (W == 4) {
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            ss += v.x * v.x;
+            ss += v.y * v.y;
+            ss += v.z * v.z;
+            ss += v.w * v.w;
+        }
+    } else {
+        for (int c = threadIdx.x; c < E; c += blockDim.x) ss += xr[c] * xr[c];
+    }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)E + eps);
     const int slot = taps > 0 ? row_slot[r] : -1;
     const bool conv = taps > 0 && slot >= 0 && slot < n_slots;
-    for (int c = threadIdx.x; c < E; c += blockDim.x) {
-        const float v = xr[c];
-        const T h = from_f32<T>(v * scale * w1[c]);
-        if (out2) out2[(size_t)r * E + c] = from_f32<T>(v * scale * w2[c]);
-        if (!conv) {
-            out1[(size_t)r * E + c] = h;
-            continue;
+    if (W == 4 && !conv) {
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            const float4 g = *reinterpret_cast<const float4*>(w1 + c);
+            const float o1[4] = {v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w};
+            store_values<T, 4>(out1 + (size_t)r * E + c, o1);
+            if (out2) {
+                const float4 g2 = *reinterpret_cast<const float4*>(w2 + c);
+                const float o2[4] = {v.x * scale * g2.x, v.y * scale * g2.y, v.z * scale * g2.z, v.w * scale * g2.w};
+                store_values<T, 4>(out2 + (size_t)r * E + c, o2);
+            }
         }
-        T* tl = tail + (size_t)slot * (taps - 1) * E + c;
-        const float own = to_f32(h);
-        float acc = 0.0f;
-        for (int j = 0; j + 1 < taps; j++) acc = fmaf(cw[(size_t)j * E + c], to_f32(tl[(size_t)j * E]), acc);
-        acc = fmaf(cw[(size_t)(taps - 1) * E + c], own, acc);
-        out1[(size_t)r * E + c] = from_f32<T>(own + acc);
-        if (update_tail) {
-            for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
-            if (taps > 1) tl[(size_t)(taps - 2) * E] = h;
+        return;
+    }
+    for (int c0 = W * threadIdx.x; c0 < E; c0 += W * blockDim.x) {
+        for (int c = c0; c < c0 + W; c++) {
+            const float v = xr[c];
+            const T h = from_f32<T>(v * scale * w1[c]);
+            if (out2) out2[(size_t)r * E + c] = from_f32<T>(v * scale * w2[c]);
+            if (!conv) {
+                out1[(size_t)r * E + c] = h;
+                continue;
+            }
+            T* tl = tail + (size_t)slot * (taps - 1) * E + c;
+            const float own = to_f32(h);
+            float acc = 0.0f;
+            for (int j = 0; j + 1 < taps; j++) acc = fmaf(cw[(size_t)j * E + c], to_f32(tl[(size_t)j * E]), acc);
+            acc = fmaf(cw[(size_t)(taps - 1) * E + c], own, acc);
+            out1[(size_t)r * E + c] = from_f32<T>(own + acc);
+            if (update_tail) {
+                for (int i = 0; i + 2 < taps; i++) tl[(size_t)i * E] = tl[(size_t)(i + 1) * E];
+                if (taps > 1) tl[(size_t)(taps - 2) * E] = h;
+            }
         }
     }
 }
@@ -163,7 +241,7 @@ static int launch_pair(const float* x, const float* w1, const float* w2, const f
     BC_CHECK_ARG(taps == 0 || (cw && row_slot && (tail || taps == 1)), "norm_pair: the convolution needs its weights, the rows' slots and the tail");
     if (rows == 0) return BC_OK;
     // The block's size depends on the row's width alone, never on the number of rows: a row's statistic is the same bits in any batch.
-    const int threads = E >= 4096 ? 1024 : E >= 1024 ? 512 : 256;
+    const int threads = E >= 8192 ? 1024 : E >= 2048 ? 512 : 256;
     bc_launch(norm_pair_conv_kernel<T>, dim3(rows), dim3(threads), 0, s, x, w1, w2, cw, (T*)tail, row_slot, (T*)out1, (T*)out2, E, eps, taps,
               n_slots, update_tail);
     BC_LAUNCH_STATUS();
@@ -191,12 +269,21 @@ static int launch(const void* h, const float* w, void* tail, const int* seq_rows
     const int fused = write_tail && max_new == 1;
     constexpr int V = 16 / (int)sizeof(T);
     const bool wide = E % V == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)tail % 16 == 0;
-    if (wide)
+    const dim3 rows_grid((max_new + SC_ROWS - 1) / SC_ROWS, seqs, (E / V + SC_THREADS - 1) / SC_THREADS);
+#define SC_CASE(TAPS)                                                                                                                   \
+    case TAPS:                                                                                                                          \
+        bc_launch(short_conv_rows_kernel<T, V, TAPS>, rows_grid, dim3(SC_THREADS), 0, s, (const T*)h, w, (const T*)tail, seq_rows, seq_slot, \
+                  (T*)out, E, n_slots);                                                                                                 \
+        break;
+    if (wide && max_new > 1 && taps >= 2 && taps <= 8) {
+        switch (taps) { SC_CASE(2) SC_CASE(3) SC_CASE(4) SC_CASE(5) SC_CASE(6) SC_CASE(7) SC_CASE(8) }
+    } else if (wide)
         bc_launch(short_conv_kernel<T, V>, dim3(max_new, seqs, (E / V + SC_THREADS - 1) / SC_THREADS), dim3(SC_THREADS), 0, s, (const T*)h, w,
                   (T*)tail, seq_rows, seq_slot, (T*)out, E, taps, n_slots, fused);
     else
         bc_launch(short_conv_kernel<T, 1>, dim3(max_new, seqs, chunks), dim3(SC_THREADS), 0, s, (const T*)h, w, (T*)tail, seq_rows, seq_slot,
                   (T*)out, E, taps, n_slots, fused);
+#undef SC_CASE
     if (write_tail && !fused && taps > 1) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {
