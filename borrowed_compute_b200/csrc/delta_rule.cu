@@ -102,7 +102,7 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, int stride,
                                      float decay_scale, float key_eps) {
     extern __shared__ float th[];        // tanh of the inner projection, [DP_ROWS][inner]
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int row0 = blockIdx.x * DP_ROWS, head = blockIdx.y, HD = H * D;
     const int n = min(DP_ROWS, rows - row0);
@@ -168,7 +168,7 @@ delta_scan_kernel(const float* __restrict__ proj, int stride, const float* __res
     constexpr int VEC = DR_STEPS * DP;                              // one staged vector: [DR_STEPS][DP]
     constexpr int BUF = 5 * VEC + DR_STEPS * DR_BLOCK_COLS + DR_STEPS * 2;
     __shared__ __align__(16) float sm[2][BUF];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int sq = blockIdx.x, head = blockIdx.y, HD = H * D;
     const int slot = seq_slot[sq];
@@ -268,7 +268,7 @@ template <class T>
 __global__ void delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride, const float* __restrict__ weight,
                                     T* __restrict__ out, int rows, int H, int D, float eps) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int row0 = blockIdx.x * DP_ROWS, head = blockIdx.y, HD = H * D;
     const int n = min(DP_ROWS, rows - row0);
@@ -300,7 +300,7 @@ delta_step_kernel(const float* __restrict__ proj, int stride, const float* __res
     float* th = sm;
     float* sw = th + ((inner + 3) & ~3);      // 16-byte aligned: the dynamic shared memory is, and inner is rounded up to 4
     float *su = sw + DP, *sb = su + DP, *sr = sb + DP, *sk = sr + DP, *so = sk + DP;
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y, HD = H * D;
     const int slot = row_slot[row];

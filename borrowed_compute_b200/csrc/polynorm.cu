@@ -9,7 +9,7 @@ template <class T>
 __global__ void __launch_bounds__(1024) polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, T* __restrict__ out, int F,
                                                        float eps) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];     // weights: written by no kernel
     pdl_wait();
     const float* zr = z + (size_t)blockIdx.x * F;

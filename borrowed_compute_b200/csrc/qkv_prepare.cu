@@ -32,7 +32,7 @@ qkv_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ bias
                    T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int D, int DV, int rot, float eps, int normed,
                    int write_cache) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int r = blockIdx.x;
     const int nq = H * D, nk = G * D, nv = G * DV;

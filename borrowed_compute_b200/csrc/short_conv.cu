@@ -56,7 +56,7 @@ template <class T, int V>
 __global__ void __launch_bounds__(SC_THREADS)
 short_conv_kernel(const T* __restrict__ h, const float* __restrict__ w, T* __restrict__ tail, const int* __restrict__ seq_rows,
                   const int* __restrict__ seq_slot, T* __restrict__ out, int E, int taps, int n_slots, int update_tail) {
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int tok = blockIdx.x, sq = blockIdx.y;
     const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
@@ -103,7 +103,7 @@ template <class T, int V, int TAPS>
 __global__ void __launch_bounds__(SC_THREADS)
 short_conv_rows_kernel(const T* __restrict__ h, const float* __restrict__ w, const T* __restrict__ tail, const int* __restrict__ seq_rows,
                        const int* __restrict__ seq_slot, T* __restrict__ out, int E, int n_slots) {
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int tok0 = blockIdx.x * SC_ROWS, sq = blockIdx.y;
     const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
@@ -150,7 +150,7 @@ template <class T>
 __global__ void __launch_bounds__(SC_THREADS)
 short_conv_tail_kernel(const T* __restrict__ h, T* __restrict__ tail, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot,
                        int E, int taps, int n_slots) {
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int sq = blockIdx.x;
     const int c = blockIdx.y * SC_THREADS + threadIdx.x;
@@ -174,7 +174,7 @@ norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1,
                       T* __restrict__ tail, const int* __restrict__ row_slot, T* __restrict__ out1, T* __restrict__ out2, int E, float eps,
                       int taps, int n_slots, int update_tail) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_if_resident();
     pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)r * E;
