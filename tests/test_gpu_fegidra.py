@@ -404,6 +404,59 @@ def test_a_far_key_in_the_delta_state():
     close(run_cut(eng, toks, [64, 2, 200]), ref, "float32")
 
 
+def drawn_config(seed):
+    """A configuration drawn from sizes that no other test uses: widths and vocabularies that are no multiple of 8,
+    heads of 4 to 128 channels, values wider and narrower than keys, chunks from 1 to beyond the sequence, 1 to 9
+    taps, layers without feed-forward, attention without rotation or without chunks, any order of layers."""
+    rng = np.random.default_rng(seed)
+    layers = []
+    for _ in range(int(rng.integers(1, 5))):
+        ff = None if rng.random() < 0.2 else int(rng.choice([16, 40, 52, 96, 130, 256]))
+        if rng.random() < 0.5:
+            layers.append(pf.delta_layer(int(rng.choice([1, 2, 3, 5])), int(rng.choice([4, 8, 12, 16, 20, 32, 40, 64])), int(rng.choice([1, 3, 8, 16, 33])), ff))
+            continue
+        G = int(rng.choice([1, 2, 3]))
+        D = int(rng.choice([8, 16, 24, 32, 40, 64, 128]))
+        rot = min(int(rng.choice([0, 2, 4, 8, D])), D) // 2 * 2
+        L = pf.attention_layer(G * int(rng.choice([1, 2, 3, 4])), G, D, int(rng.choice([4, 8, 16, 24, 32, 64, 128])),
+                               int(rng.choice([1, 2, 7, 16, 33, 64, 65, 100, 128, 1000])), max(rot, 2), float(rng.choice([100.0, 10000.0, 1e6])),
+                               float(rng.choice([0.05, 0.125, 0.3])), ff)
+        if rot == 0:
+            del L["mixer"]["rot"]
+        if rng.random() < 0.15:
+            del L["mixer"]["mask"]
+        layers.append(L)
+    cfg = {"architecture": "Fegidra", "vocab": int(rng.choice([17, 64, 100, 257])), "width": int(rng.choice([24, 40, 48, 64, 72, 100, 128, 136])),
+           "norm": {"eps": float(rng.choice([1e-5, 1e-6, 1e-3]))}, "canon": {"taps": int(rng.choice([1, 2, 3, 4, 5, 7, 9]))}, "layers": layers}
+    return cfg, rng
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_drawn_configurations_in_a_batch(seed):
+    """Two or three unequal prompts of a drawn configuration start together and decode together, in float32."""
+    from borrowed_compute_b200.engine import StepEntry
+
+    cfg, rng = drawn_config(seed)
+    w = pf.make_weights(cfg, 100 + seed)
+    n = int(rng.integers(2, 4))
+    lens, more = [int(rng.integers(1, 110)) for _ in range(n)], [int(rng.integers(1, 14)) for _ in range(n)]
+    seqs = [tokens_for(seed * 10 + i, a + b, cfg["vocab"]) for i, (a, b) in enumerate(zip(lens, more))]
+    eng = engine_for(cfg, w, "float32", max_tokens=1024, max_slots=3, max_seq=192)
+    slots = [eng.acquire() for _ in seqs]
+    out = eng.step([StepEntry(s, q[:a], tuple(range(a))) for s, q, a in zip(slots, seqs, lens)]).cpu().numpy()
+    got, at = [], 0
+    for a in lens:
+        got.append([out[at:at + a]])
+        at += a
+    for step in range(max(more)):
+        live = [i for i in range(n) if step < more[i]]
+        out = eng.step([StepEntry(slots[i], [seqs[i][lens[i] + step]], (0,)) for i in live]).cpu().numpy()
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+    for i in range(n):
+        close(np.concatenate(got[i]), pf.logits(cfg, w, seqs[i]), "float32", f"{json.dumps(cfg)}: sequence {i}")
+
+
 def test_greedy_generation_through_the_entry_point(tmp_path):
     """A folder whose config.json leaves the decay's inner width to the tensors' shapes, loaded by Local and by
     the command line; greedy tokens of a batch of unequal prompts against the plain loop."""
