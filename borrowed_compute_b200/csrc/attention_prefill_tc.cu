@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(64 + NT * 128, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, const int* __restrict__ seq_rows,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
-                            int max_pages, int n_pages, int window, float scale_log2) {
+                            int max_pages, int n_pages, int window, int chunk, float scale_log2) {
     constexpr int THREADS = 64 + NT * 128;
     constexpr int STAGES = APT_STAGES(D, NT);
     // P in shared memory only (APT_P_TMEM 0): two P tiles a query tile let the softmax of page
@@ -122,7 +122,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tok_end = min(n_new, tok0 + tokens_per_block);
     const int* pages = page_table + (size_t)slot * max_pages;
     // Pages this block reads: from the first position its first token sees to its last token's own.
-    const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
+    // With chunks a position sees only its own chunk, counted from position 0: nothing before the chunk of the first token.
+    const int window_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
+    const int first_pos = chunk > 0 ? max(window_pos, (start + tok0) / chunk * chunk) : window_pos;
     const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
     const int n_tiles = t_end - t_begin;
     const int last_pos = start + n_new - 1;               // the last position the sequence holds after this step
@@ -263,8 +265,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int tok = tok0 + row / group, head = g * group + row % group;
         const bool live = row / group < tokens_per_block && tok < n_new;
         const int pos = start + tok;
-        const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        const int window_lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        const int lo = chunk > 0 ? max(window_lo, pos / chunk * chunk) : window_lo;
         const int warp_first_pos = start + tok0 + (t * APT_ROWS + 32 * q) / group;   // the smallest position a row of this warp has
+        // Where the chunk of this warp's last row begins: a page that starts there or later lies in every row's chunk.
+        const int warp_chunk_lo = chunk > 0 ? (start + tok0 + (t * APT_ROWS + 32 * q + 31) / group) / chunk * chunk : 0;
         const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
         const uint32_t o_addr = lane_base + O_COL + t * D;
         float m_used = -INFINITY, l = 0.0f;
@@ -284,7 +289,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool page_ok = page_at(j) >= 0;
             // A page that ends at or before the position of this warp's first row is seen whole
             // by all of its rows (padding rows are never written): no mask to work out.
-            const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= warp_first_pos;
+            const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= warp_first_pos && tile * BC_PAGE >= warp_chunk_lo;
             float tmax = -INFINITY;
             if (whole) {
                 // Two chains of three-input maxima: 32 instructions, each chain 16 long.
@@ -465,7 +470,7 @@ static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_ro
 template <int D, int NT>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
-                  int window, float scale, cudaStream_t s) {
+                  int window, int chunk, float scale, cudaStream_t s) {
     constexpr int DB = D / 64;
     constexpr int STAGES = APT_STAGES(D, NT), PB = APT_PB(D, NT);
     constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * PB * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
@@ -482,7 +487,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     const int tokens_per_block = NT * APT_ROWS / (H / G);
     dim3 grid(G, (max_new + tokens_per_block - 1) / tokens_per_block, seqs);
     cudaError_t e = bc_launch(attention_prefill_tc_kernel<D, NT>, grid, dim3(64 + NT * 128), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows,
-                              seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, scale * 1.4426950408889634f);
+                              seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk, scale * 1.4426950408889634f);
     if (e != cudaSuccess) {
         bc_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -514,14 +519,15 @@ extern "C" int bc_attention_prefill_tc_accepts(int H, int G, int D) {
 // (TMA reads past them as zeros).  q and the caches 16-byte aligned, q_stride a multiple of 8.
 extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int total_rows, const void* k_cache, const void* v_cache,
                                             const int* page_table, const int* seq_rows, const int* seq_slot, const int* seq_start, void* out,
-                                            int seqs, int max_new, int H, int G, int D, int max_pages, int n_pages, int window, float scale,
-                                            cudaStream_t s) {
+                                            int seqs, int max_new, int H, int G, int D, int max_pages, int n_pages, int window, int chunk,
+                                            float scale, cudaStream_t s) {
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && total_rows >= 0, "attention_prefill_tc: bad sizes seqs=%d max_new=%d rows=%d", seqs,
                  max_new, total_rows);
     BC_CHECK_ARG(bc_attention_prefill_tc_accepts(H, G, D), "attention_prefill_tc: H=%d G=%d D=%d is outside what this kernel takes "
                  "(at most %d heads a kv head, head size 64 or 128)", H, G, D, APT_ROWS);
     BC_CHECK_ARG(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
                  "attention_prefill_tc: q, out and the caches must be 16-byte aligned, the row stride a multiple of 8");
+    BC_CHECK_ARG(window >= 0 && chunk >= 0, "attention_prefill_tc: bad window %d or chunk %d", window, chunk);
     BC_CHECK_ARG(n_pages > 0 && max_new / (APT_ROWS / (H / G)) < 65535, "attention_prefill_tc: bad pages %d or too many new rows %d", n_pages, max_new);
     if (seqs == 0 || max_new == 0 || total_rows == 0) return BC_OK;
     CUtensorMap mq, mk, mv;
@@ -536,7 +542,7 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
     const long long cache_rows = (long long)n_pages * G * BC_PAGE;
     if ((st = bc_cached_cache_map(&mk, k_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
     if ((st = bc_cached_cache_map(&mv, v_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
-#define APT_GO(DD, NN) return launch<DD, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s)
+#define APT_GO(DD, NN) return launch<DD, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, s)
     if (D == 64 && nt == 1) APT_GO(64, 1);
     if (D == 64) APT_GO(64, 2);
     if (nt == 1) APT_GO(128, 1);

@@ -890,11 +890,12 @@ def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Op
 def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                       seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
                       heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-                      use_tc: Optional[bool] = None) -> None:
+                      use_tc: Optional[bool] = None, chunk: int = 0) -> None:
     """Causal attention of every sequence's new rows against its cached positions (which
     include the new rows' own keys and values), bf16.  Head sizes 64 and 128 run on the
     tcgen05 tensor cores, 128 query rows a block (scores and output accumulate in TMEM);
-    other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other."""
+    other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other.
+    ``chunk`` > 0: a position sees only those of its own chunk of that many positions, counted from position 0."""
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -923,7 +924,11 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
     if use_tc:
         _call(_fn("bc_attention_prefill_tc_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
               _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads),
-              _c_int(head_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
+              _c_int(head_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+        return
+    if chunk > 0:
+        attention_tiles(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, heads, kv_heads, head_dim,
+                        head_dim, window=window, chunk=chunk, scale=scale)
         return
     _call(_fn("bc_attention_prefill_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),

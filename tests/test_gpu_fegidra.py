@@ -386,6 +386,32 @@ def test_tiles_against_rows_in_bfloat16():
     assert np.abs(tiles - rows).max() <= 0.5 * tol("bfloat16", rows)
 
 
+def test_prompts_on_tcgen05_tiles_when_values_are_as_wide_as_keys():
+    """Heads of 64 with values of 64: prompts and portions take the tcgen05 kernel under the chunk mask (chunks of
+    100 cut pages and query tiles), single rows the mma.sync tiles; against the oracle, and against the same steps
+    with every prompt kept on the mma.sync tiles."""
+    from borrowed_compute_b200.parts import attention_kv
+
+    cfg = {"architecture": "Fegidra", "vocab": 80, "width": 64, "norm": {"eps": 1e-5}, "canon": {"taps": 2}, "layers": [
+        pf.attention_layer(6, 2, 64, 64, 100, 16, 10000.0, 0.125, 96), pf.delta_layer(2, 16, 4, None),
+        pf.attention_layer(4, 4, 64, 64, 100, 64, 10000.0, 0.125, 96)]}
+    w = pf.make_weights(cfg, 21)
+    for n in w:
+        if n.endswith(("q.norm", "k.norm")):
+            w[n] = pf.bf16_round(w[n] * 2.0)
+    eng = engine_for(cfg, w, "bfloat16")
+    toks = tokens_for(34, 330, cfg["vocab"])
+    ref = pf.logits(cfg, w, toks)
+    tc = run_cut(eng, toks, [150, 99, 2, 60])
+    close(tc, ref, "bfloat16", "tcgen05 prompts")
+    attention_kv.force_tiles = True
+    try:
+        tiles = run_cut(eng, toks, [150, 99, 2, 60])
+    finally:
+        attention_kv.force_tiles = False
+    assert np.abs(tc - tiles).max() <= 0.5 * tol("bfloat16", ref)
+
+
 def test_a_far_key_in_the_delta_state():
     """One delta-rule layer with decays close to one: a token 300 positions back still shapes the output;
     decoding from the carried state must agree with the whole prompt."""

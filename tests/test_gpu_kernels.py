@@ -211,11 +211,13 @@ def test_rope_append_of_many_rows_gives_the_bits_of_few_rows(H, G, D, pairing):
     assert torch.equal(results[0][0][[3, 77, 149]], dev(qkv, torch.bfloat16)[[3, 77, 149]]), "a padding row was touched"
 
 
-def attention_reference(q, k, v, window=0):
+def attention_reference(q, k, v, window=0, chunk=0):
     """q [H, D] at the last position of k, v [T, G, D]."""
     H, D = q.shape
     T, G, _ = k.shape
     lo = max(0, T - window) if window > 0 else 0
+    if chunk > 0:
+        lo = max(lo, (T - 1) // chunk * chunk)
     out = np.zeros((H, D))
     for h in range(H):
         g = h // (H // G)
@@ -437,7 +439,7 @@ def test_tcgen05_prompt_attention_refuses_what_it_cannot_do():
     assert not ops.attention_prefill_tc_accepts(H, G, D, shifted, H * D)
 
 
-def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
+def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5, chunk=0):
     """One launch of a prompt kernel over sequences that bring new[s] rows after cached[s]
     positions (with a padding sequence among them), against the float64 formula at chosen
     rows and against the one-warp-a-row twin at all rows."""
@@ -460,8 +462,9 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
         vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
         qs_.append((r.standard_normal((n, H * D)) * q_scale).astype(np.float32))
     # what no position owns is not-a-number; under a window the pages behind the first new row's window are gone
-    poison(kp, vp, table, [c + n for c, n in zip(cached, new)],
-           drop_before=[max(0, c + 1 - window) for c in cached] if window else None)
+    # and under a chunk mask those behind the chunk the first new row lies in
+    behind = [max(max(0, c + 1 - window) if window else 0, c // chunk * chunk if chunk else 0) for c in cached]
+    poison(kp, vp, table, [c + n for c, n in zip(cached, new)], drop_before=behind if window or chunk else None)
     # sequence order in the step: 0, 1, a padding sequence, then the rest
     order = [0, 1, -1] + list(range(2, len(new)))
     seq_rows, seq_slot, seq_start, rows = [0], [], [], []
@@ -477,7 +480,7 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
     out = torch.full((total, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
     ops.attention_prefill(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table),
                           dev(np.array(seq_rows, dtype=np.int32)), dev(np.array(seq_slot, dtype=np.int32)),
-                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc)
+                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc, chunk=chunk)
     if use_tc:
         assert ops.attention_prefill_tc_status() == 0
     assert bool(torch.isfinite(out.float()).all()), "something nobody owns reached a result"
@@ -488,16 +491,16 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
             continue
         for i in range(new[s]):
             p = cached[s] + i
-            if i in (0, 1, new[s] // 2, new[s] - 2, new[s] - 1) or (p % 64) in (0, 63):
+            if i in (0, 1, new[s] // 2, new[s] - 2, new[s] - 1) or (p % 64) in (0, 63) or (chunk and (p % chunk) in (0, 1, chunk - 1)):
                 ref = attention_reference(qst[at + i].reshape(H, D), stored(ks[s][:p + 1], torch.bfloat16),
-                                          stored(vs[s][:p + 1], torch.bfloat16), window)
+                                          stored(vs[s][:p + 1], torch.bfloat16), window, chunk)
                 assert np.abs(got[at + i].reshape(H, D) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"sequence {s} row {i}"
         at += new[s]
     row_slot = np.concatenate([np.full(new[s], s, dtype=np.int32) for s in order if s >= 0])
     row_pos = np.concatenate([np.arange(cached[s], cached[s] + new[s], dtype=np.int32) for s in order if s >= 0])
     twin = torch.empty_like(out)
     ops.attention_rows(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos),
-                       dev(row_slot), twin, H, G, D, window=window)
+                       dev(row_slot), twin, H, G, D, window=window, chunk=chunk)
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -5
 
 
@@ -525,6 +528,23 @@ def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale, tiles):
         ops.set_attention_prefill_tc_tiles(tiles)
         run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], q_scale=q_scale)
         run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=q_scale)
+    finally:
+        ops.set_attention_prefill_tc_tiles(0)
+
+
+@pytest.mark.parametrize("H,G,D", [(32, 8, 128), (12, 4, 64), (10, 2, 128)])
+@pytest.mark.parametrize("chunk,window", [(1, 0), (64, 0), (100, 0), (192, 0), (333, 0), (5000, 0), (100, 70), (192, 200)])
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_attention_prefill_on_tcgen05_with_chunks(H, G, D, chunk, window, tiles):
+    """The tcgen05 prompt kernel under a chunk mask: chunks of one position, of a page, of sizes that cut pages and
+    query tiles anywhere, and beyond the sequence; alone and with a sliding window; new rows that start inside a
+    chunk whose earlier pages the cache still holds, the pages of older chunks gone and poisoned."""
+    from borrowed_compute_b200 import ops
+
+    try:
+        ops.set_attention_prefill_tc_tiles(tiles)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], chunk=chunk)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=8.0, chunk=chunk)
     finally:
         ops.set_attention_prefill_tc_tiles(0)
 
