@@ -74,7 +74,7 @@ extern "C" int bc_attention_prefill_tc_set_trace(long long* buf, int y) {
 // two groups of softmax warps give every SM sub-partition two warps to switch between while
 // one waits for TMEM, a fence or a barrier: with one tile the softmax warps, one a
 // sub-partition, are the kernel's limit.  One tile serves steps with few new rows.
-template <int D, int NT>
+template <int D, int DV, int NT>
 __global__ void __launch_bounds__(64 + NT * 128, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, const int* __restrict__ seq_rows,
@@ -87,6 +87,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // memory has room for one only, and the softmax then waits for that product.
     constexpr int PB = APT_PB(D, NT);
     constexpr int DB = D / 64;                         // 64-element blocks of the head size
+    constexpr int DVB = DV / 64;                       // and of a head's values (a stage keeps room for DB of them)
     constexpr int ROW_BLOCK = APT_ROWS * 128;          // bytes of a [128 rows][64 elements] block
     constexpr int KV_BLOCK = BC_PAGE * 128;            // bytes of a [64 positions][64 elements] block
     constexpr int Q_BYTES = DB * NT * ROW_BLOCK;       // per 64 elements: the rows of all tiles, one after another
@@ -94,6 +95,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int O_COL = NT * 128;                    // TMEM columns: scores of (tile t, buffer b) from (2 t + b) 64, outputs from O_COL + t D
     constexpr int TMEM_COLS = NT == 1 ? 256 : 512;
     static_assert(D == 64 || D == 128, "head size 64 or 128");
+    static_assert((DV == 64 || DV == 128) && DV <= D, "values of 64 or 128, no wider than the keys");
     static_assert(NT == 1 || NT == 2, "one or two query tiles");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -185,17 +187,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 const int y = (page * G + g) * BC_PAGE;
                 const uint32_t dst = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
-                mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
-                for (int b = 0; b < DB; b++) {
-                    tma_load_2d(dst + b * KV_BLOCK, &map_k, kv_full0 + 8 * s, b * 64, y);
-                    tma_load_2d(dst + (DB + b) * KV_BLOCK, &map_v, kv_full0 + 8 * s, b * 64, y);
-                }
+                mbar_expect_tx(kv_full0 + 8 * s, (DB + DVB) * KV_BLOCK);
+                for (int b = 0; b < DB; b++) tma_load_2d(dst + b * KV_BLOCK, &map_k, kv_full0 + 8 * s, b * 64, y);
+                for (int b = 0; b < DVB; b++) tma_load_2d(dst + (DB + b) * KV_BLOCK, &map_v, kv_full0 + 8 * s, b * 64, y);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_b(BC_PAGE, false);   // S: N = 64 positions, keys k-major
-            constexpr uint32_t idesc_o = instr_desc_b(D, true);          // O: N = head size, values n-major
+            constexpr uint32_t idesc_o = instr_desc_b(DV, true);         // O: N = the values' width, values n-major
             // The operand descriptors are worked out once; an address further on is the descriptor
             // plus that many 16-byte units, so that a product costs its issuing thread an addition
             // or two (this one thread issues every product of the block: what it spends between
@@ -339,7 +339,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < D; c += 16) {
+                for (int c = 0; c < DV; c += 16) {
                     uint32_t ov[16];
                     tmem_load16(o_addr + c, ov);
                     tmem_load_wait();
@@ -401,8 +401,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int first_bad = !page_ok ? 0 : min(BC_PAGE, max(0, last_pos - tile * BC_PAGE + 1));
             if (t == 0 && first_bad < BC_PAGE) {
                 uint8_t* v_tile = kv_smem + (size_t)(j % STAGES) * STAGE_BYTES + DB * KV_BLOCK;
-                for (int c = 32 * q + lane; c < (BC_PAGE - first_bad) * DB * 8; c += 128) {
-                    const int vrow = first_bad + c / (DB * 8), within = c % (DB * 8);
+                for (int c = 32 * q + lane; c < (BC_PAGE - first_bad) * DVB * 8; c += 128) {
+                    const int vrow = first_bad + c / (DVB * 8), within = c % (DVB * 8);
                     *reinterpret_cast<uint4*>(v_tile + (within >> 3) * KV_BLOCK + vrow * 128 + (within & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
@@ -424,9 +424,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            bf16* dst = out + ((size_t)(row0 + tok) * H + head) * D;
+            bf16* dst = out + ((size_t)(row0 + tok) * H + head) * DV;
 #pragma unroll 1
-            for (int c = 0; c < D; c += 16) {
+            for (int c = 0; c < DV; c += 16) {
                 uint32_t ov[16];
                 tmem_load16(o_addr + c, ov);
                 tmem_load_wait();
@@ -467,7 +467,7 @@ static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_ro
     return BC_OK;
 }
 
-template <int D, int NT>
+template <int D, int DV, int NT>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
                   int window, int chunk, float scale, cudaStream_t s) {
@@ -477,7 +477,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     static_assert(SMEM <= APT_SMEM_LIMIT, "the ring does not fit");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, DV, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
             bc_set_error("attention_prefill_tc: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
             return (int)e;
@@ -486,7 +486,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     }
     const int tokens_per_block = NT * APT_ROWS / (H / G);
     dim3 grid(G, (max_new + tokens_per_block - 1) / tokens_per_block, seqs);
-    cudaError_t e = bc_launch(attention_prefill_tc_kernel<D, NT>, grid, dim3(64 + NT * 128), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows,
+    cudaError_t e = bc_launch(attention_prefill_tc_kernel<D, DV, NT>, grid, dim3(64 + NT * 128), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows,
                               seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk, scale * 1.4426950408889634f);
     if (e != cudaSuccess) {
         bc_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
@@ -514,17 +514,22 @@ static int g_apt_sms() {
 extern "C" int bc_attention_prefill_tc_accepts(int H, int G, int D) {
     return G > 0 && H % G == 0 && H / G <= APT_ROWS && (D == 64 || D == 128) && bc_encode_tiled_fn() != nullptr;
 }
+// The same with values DV wide: 64 or 128 and no wider than the keys.
+extern "C" int bc_attention_prefill_tc_accepts_kv(int H, int G, int D, int DV) {
+    return bc_attention_prefill_tc_accepts(H, G, D) && (DV == 64 || DV == 128) && DV <= D;
+}
 
 // The interface of bc_attention_prefill_bf16, plus total_rows: how many rows q has in all
-// (TMA reads past them as zeros).  q and the caches 16-byte aligned, q_stride a multiple of 8.
+// (TMA reads past them as zeros), and DV, the width of a head's values (v_cache [pages, G, 64, DV], out [rows, H DV]).
+// q and the caches 16-byte aligned, q_stride a multiple of 8.
 extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int total_rows, const void* k_cache, const void* v_cache,
                                             const int* page_table, const int* seq_rows, const int* seq_slot, const int* seq_start, void* out,
-                                            int seqs, int max_new, int H, int G, int D, int max_pages, int n_pages, int window, int chunk,
-                                            float scale, cudaStream_t s) {
+                                            int seqs, int max_new, int H, int G, int D, int DV, int max_pages, int n_pages, int window,
+                                            int chunk, float scale, cudaStream_t s) {
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && total_rows >= 0, "attention_prefill_tc: bad sizes seqs=%d max_new=%d rows=%d", seqs,
                  max_new, total_rows);
-    BC_CHECK_ARG(bc_attention_prefill_tc_accepts(H, G, D), "attention_prefill_tc: H=%d G=%d D=%d is outside what this kernel takes "
-                 "(at most %d heads a kv head, head size 64 or 128)", H, G, D, APT_ROWS);
+    BC_CHECK_ARG(bc_attention_prefill_tc_accepts_kv(H, G, D, DV), "attention_prefill_tc: H=%d G=%d D=%d DV=%d is outside what this kernel takes "
+                 "(at most %d heads a kv head, head size 64 or 128, values of 64 or 128 and no wider than the keys)", H, G, D, DV, APT_ROWS);
     BC_CHECK_ARG(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
                  "attention_prefill_tc: q, out and the caches must be 16-byte aligned, the row stride a multiple of 8");
     BC_CHECK_ARG(window >= 0 && chunk >= 0, "attention_prefill_tc: bad window %d or chunk %d", window, chunk);
@@ -541,12 +546,14 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
     if (st != BC_OK) return st;
     const long long cache_rows = (long long)n_pages * G * BC_PAGE;
     if ((st = bc_cached_cache_map(&mk, k_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
-    if ((st = bc_cached_cache_map(&mv, v_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
-#define APT_GO(DD, NN) return launch<DD, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, s)
-    if (D == 64 && nt == 1) APT_GO(64, 1);
-    if (D == 64) APT_GO(64, 2);
-    if (nt == 1) APT_GO(128, 1);
-    APT_GO(128, 2);
+    if ((st = bc_cached_cache_map(&mv, v_cache, cache_rows, DV, "attention_prefill_tc")) != BC_OK) return st;
+#define APT_GO(DD, VV, NN) return launch<DD, VV, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, s)
+    if (D == 64 && nt == 1) APT_GO(64, 64, 1);
+    if (D == 64) APT_GO(64, 64, 2);
+    if (DV == 64 && nt == 1) APT_GO(128, 64, 1);
+    if (DV == 64) APT_GO(128, 64, 2);
+    if (nt == 1) APT_GO(128, 128, 1);
+    APT_GO(128, 128, 2);
 #undef APT_GO
 }
 

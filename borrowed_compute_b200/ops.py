@@ -879,10 +879,13 @@ def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cac
           _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
 
 
-def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0) -> bool:
+def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0,
+                                 value_dim: Optional[int] = None) -> bool:
     """Whether the tcgen05 prompt kernel takes these sizes (head size 64 or 128, at most 128
-    heads a kv head) and, if given, this q (16-byte aligned, row stride a multiple of 8)."""
-    if not _fn("bc_attention_prefill_tc_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)):
+    heads a kv head, values of 64 or 128 and no wider than the keys) and, if given, this q
+    (16-byte aligned, row stride a multiple of 8)."""
+    if not _fn("bc_attention_prefill_tc_accepts_kv")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                                                     _c_int(head_dim if value_dim is None else value_dim)):
         return False
     return q is None or (q.data_ptr() % 16 == 0 and q_stride % 8 == 0)
 
@@ -890,12 +893,14 @@ def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Op
 def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                       seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
                       heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-                      use_tc: Optional[bool] = None, chunk: int = 0) -> None:
+                      use_tc: Optional[bool] = None, chunk: int = 0, value_dim: Optional[int] = None) -> None:
     """Causal attention of every sequence's new rows against its cached positions (which
     include the new rows' own keys and values), bf16.  Head sizes 64 and 128 run on the
     tcgen05 tensor cores, 128 query rows a block (scores and output accumulate in TMEM);
     other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other.
-    ``chunk`` > 0: a position sees only those of its own chunk of that many positions, counted from position 0."""
+    ``chunk`` > 0: a position sees only those of its own chunk of that many positions, counted from position 0.
+    ``value_dim`` (default ``head_dim``): the width of a head's values, in v_cache and in out."""
+    value_dim = head_dim if value_dim is None else int(value_dim)
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -904,10 +909,11 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
     _need(seq_slot, "seq_slot", torch.int32)
     _need(seq_start, "seq_start", torch.int32)
     _need(out, "out", torch.bfloat16)
-    if out.shape[1] != heads * head_dim:
-        raise KernelError(f"attention: out width {out.shape[1]} is not heads * head_dim")
-    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
-        raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    if out.shape[1] != heads * value_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * value_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], kv_heads, PAGE, value_dim):
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)} and {tuple(v_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}] "
+                          f"and values {value_dim} wide")
     if seq_rows.numel() < seqs + 1 or seq_slot.numel() < seqs or seq_start.numel() < seqs:
         raise KernelError("attention_prefill: fewer sequence entries than sequences")
     if scale is None:
@@ -920,15 +926,16 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
         _bounds("attention_prefill: a sequence's last position + 1", ends, page_table.shape[1] * PAGE + 1)
         _bounds("attention_prefill: page_table", page_table, k_cache.shape[0], lowest=-1)
     if use_tc is None:
-        use_tc = attention_prefill_tc_accepts(heads, kv_heads, head_dim, q, q_stride)
+        use_tc = attention_prefill_tc_accepts(heads, kv_heads, head_dim, q, q_stride, value_dim)
     if use_tc:
         _call(_fn("bc_attention_prefill_tc_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
               _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads),
-              _c_int(head_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+              _c_int(head_dim), _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk),
+              _c_float(scale), _stream())
         return
-    if chunk > 0:
+    if chunk > 0 or value_dim != head_dim:
         attention_tiles(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, heads, kv_heads, head_dim,
-                        head_dim, window=window, chunk=chunk, scale=scale)
+                        value_dim, window=window, chunk=chunk, scale=scale)
         return
     _call(_fn("bc_attention_prefill_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),

@@ -386,15 +386,15 @@ def test_tiles_against_rows_in_bfloat16():
     assert np.abs(tiles - rows).max() <= 0.5 * tol("bfloat16", rows)
 
 
-def test_prompts_on_tcgen05_tiles_when_values_are_as_wide_as_keys():
-    """Heads of 64 with values of 64: prompts and portions take the tcgen05 kernel under the chunk mask (chunks of
-    100 cut pages and query tiles), single rows the mma.sync tiles; against the oracle, and against the same steps
-    with every prompt kept on the mma.sync tiles."""
+def test_prompts_on_tcgen05_tiles():
+    """Heads of 64 with values of 64, and of 128 with values of 64: prompts and portions take the tcgen05 kernel
+    under the chunk mask (chunks of 100 cut pages and query tiles), single rows the mma.sync tiles; against the
+    oracle, and against the same steps with every prompt kept on the mma.sync tiles."""
     from borrowed_compute_b200.parts import attention_kv
 
     cfg = {"architecture": "Fegidra", "vocab": 80, "width": 64, "norm": {"eps": 1e-5}, "canon": {"taps": 2}, "layers": [
         pf.attention_layer(6, 2, 64, 64, 100, 16, 10000.0, 0.125, 96), pf.delta_layer(2, 16, 4, None),
-        pf.attention_layer(4, 4, 64, 64, 100, 64, 10000.0, 0.125, 96)]}
+        pf.attention_layer(4, 4, 128, 64, 100, 64, 10000.0, 0.09, 96)]}
     w = pf.make_weights(cfg, 21)
     for n in w:
         if n.endswith(("q.norm", "k.norm")):

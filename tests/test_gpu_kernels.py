@@ -212,13 +212,13 @@ def test_rope_append_of_many_rows_gives_the_bits_of_few_rows(H, G, D, pairing):
 
 
 def attention_reference(q, k, v, window=0, chunk=0):
-    """q [H, D] at the last position of k, v [T, G, D]."""
+    """q [H, D] at the last position of k [T, G, D], v [T, G, DV]."""
     H, D = q.shape
     T, G, _ = k.shape
     lo = max(0, T - window) if window > 0 else 0
     if chunk > 0:
         lo = max(lo, (T - 1) // chunk * chunk)
-    out = np.zeros((H, D))
+    out = np.zeros((H, v.shape[2]))
     for h in range(H):
         g = h // (H // G)
         s = k[lo:, g, :] @ q[h] / math.sqrt(D)
@@ -439,27 +439,28 @@ def test_tcgen05_prompt_attention_refuses_what_it_cannot_do():
     assert not ops.attention_prefill_tc_accepts(H, G, D, shifted, H * D)
 
 
-def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5, chunk=0):
+def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5, chunk=0, DV=None):
     """One launch of a prompt kernel over sequences that bring new[s] rows after cached[s]
     positions (with a padding sequence among them), against the float64 formula at chosen
     rows and against the one-warp-a-row twin at all rows."""
     from borrowed_compute_b200 import ops
 
+    DV = D if DV is None else DV
     width = max((c + n + 63) // 64 for c, n in zip(cached, new)) + 1
     n_pages = sum((c + n + 63) // 64 for c, n in zip(cached, new)) + 3
     r = rng(H * 100 + D + 1)
     free = list(r.permutation(n_pages))
     table = np.full((len(new), width), -1, dtype=np.int32)
     kp = np.zeros((n_pages, G, 64, D), dtype=np.float32)
-    vp = np.zeros_like(kp)
+    vp = np.zeros((n_pages, G, 64, DV), dtype=np.float32)
     ks, vs, qs_ = [], [], []
     for s, (c, n) in enumerate(zip(cached, new)):
         pages = [int(free.pop()) for _ in range((c + n + 63) // 64)]
         table[s, :len(pages)] = pages
-        k, v = r.standard_normal((c + n, G, D)).astype(np.float32), r.standard_normal((c + n, G, D)).astype(np.float32)
+        k, v = r.standard_normal((c + n, G, D)).astype(np.float32), r.standard_normal((c + n, G, DV)).astype(np.float32)
         ks.append(k), vs.append(v)
         kp += paged(k, pages, G, D, n_pages, torch.bfloat16)
-        vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
+        vp += paged(v, pages, G, DV, n_pages, torch.bfloat16)
         qs_.append((r.standard_normal((n, H * D)) * q_scale).astype(np.float32))
     # what no position owns is not-a-number; under a window the pages behind the first new row's window are gone
     # and under a chunk mask those behind the chunk the first new row lies in
@@ -477,10 +478,10 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5, chu
             rows.append(qs_[s])
     q = np.concatenate(rows)
     total = q.shape[0]
-    out = torch.full((total, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((total, H * DV), 9.0, dtype=torch.bfloat16, device="cuda")
     ops.attention_prefill(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table),
                           dev(np.array(seq_rows, dtype=np.int32)), dev(np.array(seq_slot, dtype=np.int32)),
-                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc, chunk=chunk)
+                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc, chunk=chunk, value_dim=DV)
     if use_tc:
         assert ops.attention_prefill_tc_status() == 0
     assert bool(torch.isfinite(out.float()).all()), "something nobody owns reached a result"
@@ -494,13 +495,13 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5, chu
             if i in (0, 1, new[s] // 2, new[s] - 2, new[s] - 1) or (p % 64) in (0, 63) or (chunk and (p % chunk) in (0, 1, chunk - 1)):
                 ref = attention_reference(qst[at + i].reshape(H, D), stored(ks[s][:p + 1], torch.bfloat16),
                                           stored(vs[s][:p + 1], torch.bfloat16), window, chunk)
-                assert np.abs(got[at + i].reshape(H, D) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"sequence {s} row {i}"
+                assert np.abs(got[at + i].reshape(H, DV) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"sequence {s} row {i}"
         at += new[s]
     row_slot = np.concatenate([np.full(new[s], s, dtype=np.int32) for s in order if s >= 0])
     row_pos = np.concatenate([np.arange(cached[s], cached[s] + new[s], dtype=np.int32) for s in order if s >= 0])
     twin = torch.empty_like(out)
     ops.attention_rows(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos),
-                       dev(row_slot), twin, H, G, D, window=window, chunk=chunk)
+                       dev(row_slot), twin, H, G, D, window=window, chunk=chunk, value_dim=DV)
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -5
 
 
@@ -532,19 +533,22 @@ def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale, tiles):
         ops.set_attention_prefill_tc_tiles(0)
 
 
-@pytest.mark.parametrize("H,G,D", [(32, 8, 128), (12, 4, 64), (10, 2, 128)])
-@pytest.mark.parametrize("chunk,window", [(1, 0), (64, 0), (100, 0), (192, 0), (333, 0), (5000, 0), (100, 70), (192, 200)])
+@pytest.mark.parametrize("H,G,D,DV", [(32, 8, 128, 128), (12, 4, 64, 64), (10, 2, 128, 128), (16, 4, 128, 64), (3, 1, 128, 64)])
+@pytest.mark.parametrize("chunk,window", [(0, 0), (1, 0), (64, 0), (100, 0), (192, 0), (333, 0), (5000, 0), (100, 70), (192, 200)])
 @pytest.mark.parametrize("tiles", [1, 2])
-def test_attention_prefill_on_tcgen05_with_chunks(H, G, D, chunk, window, tiles):
+def test_attention_prefill_on_tcgen05_with_chunks(H, G, D, DV, chunk, window, tiles):
     """The tcgen05 prompt kernel under a chunk mask: chunks of one position, of a page, of sizes that cut pages and
     query tiles anywhere, and beyond the sequence; alone and with a sliding window; new rows that start inside a
-    chunk whose earlier pages the cache still holds, the pages of older chunks gone and poisoned."""
+    chunk whose earlier pages the cache still holds, the pages of older chunks gone and poisoned.  Also with values
+    half as wide as the keys (their own plane of the cache, their own width of the output)."""
     from borrowed_compute_b200 import ops
 
+    assert ops.attention_prefill_tc_accepts(H, G, D, value_dim=DV)
+    assert not ops.attention_prefill_tc_accepts(8, 2, 64, value_dim=128) and not ops.attention_prefill_tc_accepts(8, 2, 128, value_dim=32)
     try:
         ops.set_attention_prefill_tc_tiles(tiles)
-        run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], chunk=chunk)
-        run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=8.0, chunk=chunk)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], chunk=chunk, DV=DV)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=8.0, chunk=chunk, DV=DV)
     finally:
         ops.set_attention_prefill_tc_tiles(0)
 
