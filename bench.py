@@ -755,7 +755,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
     ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra"],
-                    help="run one of the further workloads alone and print its figures (not the contract's line)")
+                    help="run one of the further workloads alone and print its figures (not the default run's one JSON line)")
     ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra: which sizes")
     args = ap.parse_args()
     if args.impl == "reference":
