@@ -39,6 +39,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 
     pdl_launch_dependents();
     pdl_wait();
+    PDL_FRESH(q); PDL_FRESH(k_cache); PDL_FRESH(v_cache);
     const int g = blockIdx.x, sq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;

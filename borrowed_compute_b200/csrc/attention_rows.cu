@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
     __shared__ __align__(16) float qs[WARPS][MAX_D];
     pdl_launch_dependents();
     pdl_wait();
+    PDL_FRESH(q); PDL_FRESH(k_cache); PDL_FRESH(v_cache);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = blockIdx.x, h = blockIdx.y * WARPS + warp;
     if (h >= H) return;

@@ -47,6 +47,10 @@ typedef __nv_bfloat16 bf16;
 // Without the attribute both calls do nothing.
 extern int g_bc_pdl;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// After pdl_wait(), for every pointer to what an earlier kernel wrote: the compiler forgets where the pointer came from, so
+// no load through it can be moved above the wait.  (A `const T* __restrict__` parameter is taken for memory that nobody
+// writes while the kernel runs; loads through one that stood in straight-line code after the wait have been moved above it.)
+#define PDL_FRESH(p) asm volatile("" : "+l"(p))
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // The same for kernels whose grids may be many times what the device holds at once (row kernels over a long

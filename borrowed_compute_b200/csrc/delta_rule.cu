@@ -104,6 +104,7 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, int stride,
     __shared__ float scratch[32];
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(proj);
     const int row0 = blockIdx.x * DP_ROWS, head = blockIdx.y, HD = H * D;
     const int n = min(DP_ROWS, rows - row0);
     for (int e = threadIdx.x; e < n * inner; e += blockDim.x) th[e] = tanhf(proj[(size_t)(row0 + e / inner) * stride + 5 * HD + e % inner]);
@@ -170,6 +171,7 @@ delta_scan_kernel(const float* __restrict__ proj, int stride, const float* __res
     __shared__ __align__(16) float sm[2][BUF];
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(proj); PDL_FRESH(decay); PDL_FRESH(unit); PDL_FRESH(removal); PDL_FRESH(dots);
     const int sq = blockIdx.x, head = blockIdx.y, HD = H * D;
     const int slot = seq_slot[sq];
     const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
@@ -270,6 +272,7 @@ __global__ void delta_finish_kernel(const float* __restrict__ o, const float* __
     __shared__ float scratch[32];
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(o); PDL_FRESH(gate);
     const int row0 = blockIdx.x * DP_ROWS, head = blockIdx.y, HD = H * D;
     const int n = min(DP_ROWS, rows - row0);
     const int d = threadIdx.x, c = head * D + d;
@@ -302,6 +305,7 @@ delta_step_kernel(const float* __restrict__ proj, int stride, const float* __res
     float *su = sw + DP, *sb = su + DP, *sr = sb + DP, *sk = sr + DP, *so = sk + DP;
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(proj);
     const int row = blockIdx.x, head = blockIdx.y, HD = H * D;
     const int slot = row_slot[row];
     if (slot < 0 || slot >= n_slots) return;

@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(1024) polynorm_kernel(const float* z, const fl
     pdl_launch_dependents_if_resident();
     const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];     // weights: written by no kernel
     pdl_wait();
+    PDL_FRESH(z);
     const float* zr = z + (size_t)blockIdx.x * F;
     T* o = out + (size_t)blockIdx.x * F;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;

@@ -34,6 +34,7 @@ qkv_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ bias
     __shared__ float scratch[32];
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(qkv);
     const int r = blockIdx.x;
     const int nq = H * D, nk = G * D, nv = G * DV;
     const float* x = qkv + (size_t)r * (nq + nk + nv);

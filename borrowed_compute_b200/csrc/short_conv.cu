@@ -58,6 +58,7 @@ short_conv_kernel(const T* __restrict__ h, const float* __restrict__ w, T* __res
                   const int* __restrict__ seq_slot, T* __restrict__ out, int E, int taps, int n_slots, int update_tail) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(h);
     const int tok = blockIdx.x, sq = blockIdx.y;
     const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
     const int slot = seq_slot[sq];
@@ -105,6 +106,7 @@ short_conv_rows_kernel(const T* __restrict__ h, const float* __restrict__ w, con
                        const int* __restrict__ seq_slot, T* __restrict__ out, int E, int n_slots) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(h); PDL_FRESH(tail);
     const int tok0 = blockIdx.x * SC_ROWS, sq = blockIdx.y;
     const int c = (blockIdx.z * SC_THREADS + threadIdx.x) * V;
     const int slot = seq_slot[sq];
@@ -152,6 +154,7 @@ short_conv_tail_kernel(const T* __restrict__ h, T* __restrict__ tail, const int*
                        int E, int taps, int n_slots) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(h);
     const int sq = blockIdx.x;
     const int c = blockIdx.y * SC_THREADS + threadIdx.x;
     const int slot = seq_slot[sq];
@@ -176,6 +179,7 @@ norm_pair_conv_kernel(const float* __restrict__ x, const float* __restrict__ w1,
     __shared__ float scratch[32];
     pdl_launch_dependents_if_resident();
     pdl_wait();
+    PDL_FRESH(x);
     const int r = blockIdx.x;
     const float* xr = x + (size_t)r * E;
     // A thread takes four neighbouring channels at a time where the width allows (W = 4), else one: which values it
