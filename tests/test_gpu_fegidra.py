@@ -171,15 +171,38 @@ def test_two_norms_with_one_statistic_and_the_convolution_riding_along(dtype, ta
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_polynorm(dtype):
+@pytest.mark.parametrize("width", [4, 6, 200, 201, 8192, 8196, 14336, 16388, 32768, 32772, 40001])
+def test_polynorm(dtype, width):
+    """Rows of every kind of width: no multiple of four (one value at a time), rows a block of 256, of 512 or of
+    1,024 threads keeps in registers, and rows too wide for that (two passes over memory)."""
     from borrowed_compute_b200 import ops
 
     rng = np.random.default_rng(3)
-    z = (rng.standard_normal((5, 200)) * np.array([[0.1], [1.0], [3.0], [10.0], [1.0]])).astype(np.float32)
+    z = (rng.standard_normal((5, width)) * np.array([[0.1], [1.0], [3.0], [10.0], [1.0]])).astype(np.float32)
     coef = np.array([0.7, -0.4, 0.2, 0.05], dtype=np.float32)
-    out = torch.empty((5, 200), dtype=torch.float32 if dtype == "float32" else torch.bfloat16, device="cuda:0")
+    out = torch.full((5, width), 9.0, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, device="cuda:0")
     ops.polynorm(torch.from_numpy(z).cuda(), torch.from_numpy(coef).cuda(), out, 1e-5)
     close(out.float().cpu().numpy(), pf.polynorm(pf.f64(z), coef, 1e-5), dtype)
+
+
+def test_polynorm_behind_a_product_that_is_still_writing():
+    """The activation right behind the product that makes its input, linked by programmatic dependent launch, many
+    times over: no load of the input may run ahead of the wait for the product."""
+    from borrowed_compute_b200 import ops
+    from borrowed_compute_b200.parts import products
+
+    rng = np.random.default_rng(4)
+    x = torch.from_numpy(rng.standard_normal((64, 256)).astype(np.float32)).cuda().bfloat16()
+    w = torch.from_numpy((rng.standard_normal((320, 256)) / 16).astype(np.float32)).cuda().bfloat16()
+    coef = torch.tensor([0.7, -0.4, 0.2, 0.05], device="cuda:0")
+    ref = pf.polynorm(pf.f64(x.float().cpu().numpy()) @ pf.f64(w.float().cpu().numpy()).T, coef.cpu().numpy(), 1e-5)
+    z = torch.empty((64, 320), dtype=torch.float32, device="cuda:0")
+    out = torch.empty((64, 320), dtype=torch.float32, device="cuda:0")
+    for _ in range(50):
+        z.fill_(1e4)                        # what an early load would see
+        products.linear(x, w, z, products.EPI_STORE_F32)
+        ops.polynorm(z, coef, out, 1e-5)
+        close(out.cpu().numpy(), ref, "float32", "behind the product")
 
 
 @pytest.mark.parametrize("heads,dim,rank", [(2, 8, 3), (3, 24, 5), (1, 32, 16), (2, 64, 7), (1, 128, 4)])
