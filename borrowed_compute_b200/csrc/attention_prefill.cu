@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(AP_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          const int* __restrict__ page_table, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G, int max_pages, int n_pages, int window,
-                         int chunk, float scale_log2) {
+                         int chunk, float scale_log2, int sink, float out_scale) {
     constexpr int CHUNKS = D / 8, VCHUNKS = DV / 8;
     constexpr int K_BYTES = 64 * D * 2, TILE_BYTES = 64 * (D + DV) * 2;      // a stage: a page of keys, then its values
     constexpr int KD = D / 16;
@@ -227,7 +227,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         if (!live[i]) continue;
-        const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
+        // A sink is one more position of score 0 that has no value: it adds 2^(0 - m) to the sum of the weights alone.
+        if (sink && m[i] != -INFINITY) l[i] += fast_exp2(-m[i]);
+        const float inv = l[i] > 0.0f ? out_scale / l[i] : 0.0f;
         bf16* dst = out + ((size_t)(row0 + tok[i]) * H + head[i]) * DV + 2 * tq;
 #pragma unroll
         for (int nd = 0; nd < ND; nd++)
@@ -238,7 +240,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 template <int D, int DV>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
-                  int window, int chunk, float scale, cudaStream_t s) {
+                  int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
     constexpr int SMEM = AP_STAGES * 64 * (D + DV) * 2;
     static bool configured = false;
     if (!configured) {
@@ -253,7 +255,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     dim3 grid(G, (max_new + tokens_per_tile - 1) / tokens_per_tile, seqs);
     bc_launch(attention_prefill_kernel<D, DV>, grid, dim3(AP_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
               (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk,
-              scale * 1.4426950408889634f);
+              scale * 1.4426950408889634f, sink, out_scale);
     BC_LAUNCH_STATUS();
 }
 
@@ -275,7 +277,7 @@ extern "C" int bc_attention_prefill_bf16(const void* q, int q_stride, const void
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
     if (seqs == 0 || max_new == 0) return BC_OK;
 #define AP_CASE(DD) \
-    case DD: return launch<DD, DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, 0, scale, s);
+    case DD: return launch<DD, DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, 0, scale, 0, 1.0f, s);
     switch (D) {
         AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
     }
@@ -292,20 +294,37 @@ extern "C" int bc_attention_prefill_kv_accepts(int H, int G, int D, int DV) {
     return (D == 32 || D == 64 || D == 128) && (DV == 16 || DV == 32 || DV == 64 || DV == 128);
 }
 
-extern "C" int bc_attention_prefill_kv_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+static int prefill_kv(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                             const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
                                             int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
-                                            cudaStream_t s) {
+                                            int sink, float out_scale, cudaStream_t s) {
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && max_new < 65535, "attention_prefill: bad sizes seqs=%d max_new=%d", seqs, max_new);
     BC_CHECK_ARG(bc_attention_prefill_kv_accepts(H, G, D, DV), "attention_prefill: H=%d G=%d D=%d DV=%d is outside what this kernel takes", H, G, D, DV);
     BC_CHECK_ARG(window >= 0 && chunk >= 0, "attention_prefill: bad window %d or chunk %d", window, chunk);
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
     if (seqs == 0 || max_new == 0) return BC_OK;
 #define AP_KV(DD, VV) \
-    if (D == DD && DV == VV) return launch<DD, VV>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, s);
+    if (D == DD && DV == VV) return launch<DD, VV>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, sink, out_scale, s);
     AP_KV(16, 16) AP_KV(32, 32) AP_KV(48, 48) AP_KV(64, 64) AP_KV(80, 80) AP_KV(96, 96) AP_KV(112, 112) AP_KV(128, 128)
     AP_KV(32, 16) AP_KV(32, 64) AP_KV(32, 128) AP_KV(64, 16) AP_KV(64, 32) AP_KV(64, 128) AP_KV(128, 16) AP_KV(128, 32) AP_KV(128, 64)
 #undef AP_KV
     bc_set_error("attention_prefill: no kernel for key width %d with value width %d", D, DV);
     return BC_ERR_ARG;
+}
+
+extern "C" int bc_attention_prefill_kv_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                            const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
+                                            int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
+                                            cudaStream_t s) {
+    return prefill_kv(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages, n_pages,
+                      window, chunk, scale, 0, 1.0f, s);
+}
+
+// The same with a sink (one more position of score 0 without a value) and a factor on the output.
+extern "C" int bc_attention_prefill_sink_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                              const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
+                                              int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
+                                              int sink, float out_scale, cudaStream_t s) {
+    return prefill_kv(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages, n_pages,
+                      window, chunk, scale, sink, out_scale, s);
 }

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
                                                                    const T* __restrict__ v_cache, const int* __restrict__ page_table,
                                                                    const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                                                                    T* __restrict__ out, int H, int G, int D, int DV, int max_pages,
-                                                                   int n_pages, int window, int chunk, float scale) {
+                                                                   int n_pages, int window, int chunk, float scale, int sink, float out_scale) {
     __shared__ __align__(16) float qs[WARPS][MAX_D];
     pdl_launch_dependents();
     pdl_wait();
@@ -121,7 +121,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
         }
         m = mn;
     }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    // A sink is one more position of score 0 that has no value: it adds e^(0 - m) to the sum of the weights alone.
+    if (sink && m != -INFINITY) l += expf(-m);
+    const float inv = l > 0.0f ? out_scale / l : 0.0f;
 #pragma unroll
     for (int j = 0; j < MAX_D / 32; j++) {
         const int d = lane + 32 * j;
@@ -132,7 +134,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
 template <class T>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
                   const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk,
-                  float scale, cudaStream_t s) {
+                  float scale, int sink, float out_scale, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && H > 0 && G > 0 && H % G == 0, "attention_rows: bad sizes rows=%d H=%d G=%d", rows, H, G);
     BC_CHECK_ARG(D > 0 && D <= MAX_D, "attention_rows: head size %d is not within 1 to %d", D, MAX_D);
     BC_CHECK_ARG(DV > 0 && DV <= MAX_D && window >= 0 && chunk >= 0, "attention_rows: bad value width %d, window %d or chunk %d", DV, window, chunk);
@@ -140,7 +142,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     if (rows == 0) return BC_OK;
     dim3 grid(rows, (H + WARPS - 1) / WARPS);
     bc_launch(attention_rows_kernel<T>, grid, dim3(WARPS * 32), 0, s, (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, page_table,
-              row_pos, row_slot, (T*)out, H, G, D, DV, max_pages, n_pages, window, chunk, scale);
+              row_pos, row_slot, (T*)out, H, G, D, DV, max_pages, n_pages, window, chunk, scale, sink, out_scale);
     BC_LAUNCH_STATUS();
 }
 
@@ -148,22 +150,35 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
 extern "C" int bc_attention_rows_f32(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                      const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int max_pages,
                                      int n_pages, int window, float scale, cudaStream_t s) {
-    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, s);
+    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, 0, 1.0f, s);
 }
 extern "C" int bc_attention_rows_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                       const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int max_pages,
                                       int n_pages, int window, float scale, cudaStream_t s) {
-    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, s);
+    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, D, max_pages, n_pages, window, 0, scale, 0, 1.0f, s);
 }
 
 // The same with values of their own width DV (out: [rows, H, DV]) and a chunk mask beside the window (0: none).
 extern "C" int bc_attention_rows_kv_f32(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                         const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
                                         int n_pages, int window, int chunk, float scale, cudaStream_t s) {
-    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, s);
+    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, 0, 1.0f, s);
 }
 extern "C" int bc_attention_rows_kv_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                          const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
                                          int n_pages, int window, int chunk, float scale, cudaStream_t s) {
-    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, s);
+    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, 0, 1.0f, s);
+}
+
+// The same with a sink (one more position of score 0 without a value, so that the weights of a row add up to less
+// than one) and a factor on the output.
+extern "C" int bc_attention_rows_sink_f32(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                          const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
+                                          int n_pages, int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+    return launch<float>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, sink, out_scale, s);
+}
+extern "C" int bc_attention_rows_sink_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                           const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int D, int DV, int max_pages,
+                                           int n_pages, int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+    return launch<bf16>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, H, G, D, DV, max_pages, n_pages, window, chunk, scale, sink, out_scale, s);
 }

@@ -1,0 +1,331 @@
+// Recurrent mixers whose state decays channel by channel and takes an outer product a token:
+//
+//     S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T        o_t = f S_t^T q_t + d v_t
+//
+// per head, with S [N, P] (N key channels, P value channels) in float, carried from token to token for every
+// sequence.  Two designs are this recurrence:
+//   - gated linear attention: a_t a vector of N decays, c = 1, d = 0, f = N^(-1/2), q, k, v per head;
+//   - the state-space dual form (Mamba-2): a_t = exp(-exp(A_log) dt_t) one number a head, c_t = dt_t, k = B and
+//     q = C shared by the heads of a group, v = x, d = D of the head.
+// Everything here is float: decays, step sizes, the state and all sums.
+//
+// Kernels:
+//   scan           the recurrence over every sequence's rows in time order
+//   ssd_prepare    causal convolution with bias and silu over [x | B | C], its last inputs kept per sequence;
+//                  dt = softplus(. + dt_bias) and the decay exp(-exp(A_log) dt)
+//   gla_decay      sigmoid(z)^(1/tau), z = W_2 inner + b, as exp(-softplus(-z) / tau)
+//   gated_norm     a row in equal parts, each over its root mean square, times a weight, the gate silu(g) before
+//                  or after the norm, a factor on the result; float in, activation type out
+#include "common.cuh"
+
+#define SCAN_NT 8          // threads that share a value channel, each with every eighth key channel
+#define SCAN_MAX_N 256
+#define SCAN_ROWS 8        // rows staged at a time
+
+// A block takes (a slice of PT value channels, head, sequence): thread (tn, p) keeps S[n][p] for n = tn, tn + 8, ...
+// in registers over the sequence's rows.  The state lies in memory value channel by value channel,
+// [slot][head][P][N], so that the eight threads of a channel read neighbouring values.  The sums of a step
+// depend on the sizes alone: the same bits whether a row comes in a prompt or alone.
+template <int NJ, bool VECTOR_DECAY>
+__global__ void __launch_bounds__(128)
+linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const float* __restrict__ k, int k_stride, int k_rep,
+                   const float* __restrict__ v, int v_stride, const float* __restrict__ decay, int d_stride,
+                   const float* __restrict__ kscale, int c_stride, const float* __restrict__ skip, float out_scale,
+                   float* __restrict__ state, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot, float* __restrict__ out,
+                   int H, int N, int P, int PT, int n_slots, int write_state) {
+    __shared__ float sq[SCAN_ROWS][SCAN_MAX_N], sk[SCAN_ROWS][SCAN_MAX_N], sd[SCAN_ROWS][VECTOR_DECAY ? SCAN_MAX_N : 1];
+    __shared__ float sv[SCAN_ROWS][16], sc[SCAN_ROWS];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(q); PDL_FRESH(k); PDL_FRESH(v); PDL_FRESH(decay); PDL_FRESH(kscale);
+    const int sidx = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * PT;
+    const int slot = seq_slot[sidx];
+    const int row0 = seq_rows[sidx], n_rows = seq_rows[sidx + 1] - row0;
+    if (slot < 0 || slot >= n_slots || n_rows <= 0) return;
+    const int tn = threadIdx.x % SCAN_NT, pl = threadIdx.x / SCAN_NT;
+    const int p = p0 + pl;
+    const bool live = pl < PT && p < P;
+    float* sp = state + (((size_t)slot * H + h) * P + (live ? p : 0)) * N;
+    float S[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const int n = tn + SCAN_NT * j;
+        S[j] = live && n < N ? sp[n] : 0.0f;
+    }
+    const float dskip = skip ? skip[h] : 0.0f;
+    const int threads = blockDim.x;
+    for (int t0 = 0; t0 < n_rows; t0 += SCAN_ROWS) {
+        const int nt = min(SCAN_ROWS, n_rows - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * N; i += threads) {
+            const int t = i / N, n = i - t * N;
+            const size_t r = (size_t)(row0 + t0 + t);
+            sq[t][n] = q[r * q_stride + (size_t)(h / q_rep) * N + n];
+            sk[t][n] = k[r * k_stride + (size_t)(h / k_rep) * N + n];
+            if (VECTOR_DECAY) sd[t][n] = decay[r * d_stride + (size_t)h * N + n];
+        }
+        for (int i = threadIdx.x; i < nt * PT; i += threads) {
+            const int t = i / PT, c = i - t * PT;
+            sv[t][c] = p0 + c < P ? v[(size_t)(row0 + t0 + t) * v_stride + (size_t)h * P + p0 + c] : 0.0f;
+        }
+        if (threadIdx.x < nt) {
+            const size_t r = (size_t)(row0 + t0 + threadIdx.x);
+            sc[threadIdx.x] = kscale ? kscale[r * c_stride + h] : 1.0f;
+            if (!VECTOR_DECAY) sd[threadIdx.x][0] = decay[r * d_stride + h];
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; t++) {
+            const float vp = pl < PT ? sv[t][pl] : 0.0f;
+            const float cv = sc[t] * vp;
+            const float a0 = VECTOR_DECAY ? 0.0f : sd[t][0];
+            float o = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const int n = tn + SCAN_NT * j;
+                if (n < N) {
+                    S[j] = fmaf(VECTOR_DECAY ? sd[t][n] : a0, S[j], sk[t][n] * cv);
+                    o = fmaf(S[j], sq[t][n], o);
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (live && tn == 0) out[(size_t)(row0 + t0 + t) * H * P + (size_t)h * P + p] = fmaf(dskip, vp, out_scale * o);
+        }
+    }
+    if (write_state && live) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int n = tn + SCAN_NT * j;
+            if (n < N) sp[n] = S[j];
+        }
+    }
+}
+
+template <bool VD>
+static int scan_launch(int NJ, dim3 grid, dim3 block, cudaStream_t s, const float* q, int q_stride, int q_rep, const float* k, int k_stride,
+                       int k_rep, const float* v, int v_stride, const float* decay, int d_stride, const float* kscale, int c_stride,
+                       const float* skip, float out_scale, float* state, const int* seq_rows, const int* seq_slot, float* out, int H, int N,
+                       int P, int PT, int n_slots, int write_state) {
+#define SCAN_CASE(J)                                                                                                                        \
+    case J:                                                                                                                                 \
+        bc_launch(linear_scan_kernel<J, VD>, grid, block, 0, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, \
+                  c_stride, skip, out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);                            \
+        break;
+    switch (NJ) {
+        SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(3) SCAN_CASE(4) SCAN_CASE(6) SCAN_CASE(8) SCAN_CASE(12) SCAN_CASE(16) SCAN_CASE(24) SCAN_CASE(32)
+    }
+#undef SCAN_CASE
+    BC_LAUNCH_STATUS();
+}
+
+// q, k: row r's vector for head h at base + r * stride + (h / rep) * N (rep heads share one); v: at v + r * v_stride + h * P;
+// decay: N values a head at decay + r * d_stride + h * N (vector_decay) or one at decay + r * d_stride + h; kscale (may be null):
+// one factor a head on the key at kscale + r * c_stride + h; skip (may be null): [H].  state: [slots, H, P, N]; out: [rows, H P].
+// Sequence i owns rows seq_rows[i] .. seq_rows[i + 1] and lives in slot seq_slot[i] (negative: skipped, its rows of out untouched).
+extern "C" int bc_linear_scan(const float* q, int q_stride, int q_rep, const float* k, int k_stride, int k_rep, const float* v, int v_stride,
+                              const float* decay, int d_stride, int vector_decay, const float* kscale, int c_stride, const float* skip,
+                              float out_scale, float* state, const int* seq_rows, const int* seq_slot, float* out, int seqs, int H, int N, int P,
+                              int n_slots, int write_state, cudaStream_t s) {
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && H > 0 && H <= 65535 && P > 0, "linear_scan: bad sizes seqs=%d H=%d P=%d", seqs, H, P);
+    BC_CHECK_ARG(N > 0 && N <= SCAN_MAX_N, "linear_scan: %d key channels are outside 1 to %d", N, SCAN_MAX_N);
+    BC_CHECK_ARG(q_rep > 0 && k_rep > 0, "linear_scan: bad sharing of q (%d) or k (%d)", q_rep, k_rep);
+    if (seqs == 0) return BC_OK;
+    int nj = (N + SCAN_NT - 1) / SCAN_NT;
+    const int have[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32};
+    for (int c : have)
+        if (c >= nj) { nj = c; break; }
+    const int PT = P >= 16 ? 16 : P;      // by the head's width alone
+    dim3 grid((P + PT - 1) / PT, H, seqs), block(PT * SCAN_NT < 32 ? 32 : (PT * SCAN_NT + 31) / 32 * 32);
+    if (vector_decay)
+        return scan_launch<true>(nj, grid, block, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, skip,
+                                 out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);
+    return scan_launch<false>(nj, grid, block, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, skip,
+                              out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);
+}
+
+// ------------------------------------------------------------------------------- ssd_prepare
+// proj: [rows, stride] float with the convolution's C channels at column `conv_at` and H step sizes at column `dt_at`.
+// Thread c < C walks a tile of a sequence's rows with the last taps - 1 inputs in registers: out[r][c] =
+// silu(bias[c] + sum_j w[j][c] in[t - taps + 1 + j]); inputs before the step's first row come from `tail`
+// [slots, taps - 1, C], zeros at a sequence's start since the cache clears a slot's state.  The block of a
+// sequence's first tile is the only reader of the old tail and writes the new one when it is done.  Threads
+// C .. C + H - 1 take the step sizes: dtda[r] = (dt[0..H), decay[0..H)).
+#define SSD_TILE 32
+#define SSD_MAX_TAPS 9
+__global__ void __launch_bounds__(128)
+ssd_prepare_kernel(const float* __restrict__ proj, int stride, int conv_at, int dt_at, const float* __restrict__ weight_t,
+                   const float* __restrict__ bias, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ tail,
+                   const int* __restrict__ seq_rows, const int* __restrict__ seq_slot, float* __restrict__ xbc, float* __restrict__ dtda, int C,
+                   int H, int taps, int n_slots, int write_tail) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(proj);
+    const int sidx = blockIdx.z, tile = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int slot = seq_slot[sidx];
+    const int row0 = seq_rows[sidx], n_rows = seq_rows[sidx + 1] - row0;
+    const int t_begin = tile * SSD_TILE;
+    if (slot < 0 || slot >= n_slots || t_begin >= n_rows || c >= C + H) return;
+    const int t_end = min(n_rows, t_begin + SSD_TILE);
+    if (c >= C) {
+        const int h = c - C;
+        const float b = dt_bias[h], a = -expf(a_log[h]);
+        for (int t = t_begin; t < t_end; t++) {
+            const float z = proj[(size_t)(row0 + t) * stride + dt_at + h] + b;
+            const float dt = z > 20.0f ? z : log1pf(expf(z));
+            float* o = dtda + (size_t)(row0 + t) * 2 * H;
+            o[h] = dt;
+            o[H + h] = expf(a * dt);
+        }
+        return;
+    }
+    const int past = taps - 1;
+    float w[SSD_MAX_TAPS], hist[SSD_MAX_TAPS - 1], old[SSD_MAX_TAPS - 1];
+#pragma unroll
+    for (int j = 0; j < SSD_MAX_TAPS; j++) w[j] = j < taps ? weight_t[(size_t)j * C + c] : 0.0f;
+    float* tl = tail + (size_t)slot * past * C + c;
+    // hist[i] is the input of relative time t_begin - past + i.
+#pragma unroll
+    for (int i = 0; i < SSD_MAX_TAPS - 1; i++) {
+        hist[i] = 0.0f;
+        old[i] = 0.0f;
+        if (i < past) {
+            const int t = t_begin - past + i;
+            if (t >= 0) hist[i] = proj[(size_t)(row0 + t) * stride + conv_at + c];
+            else if (tile == 0) hist[i] = old[i] = tl[(size_t)i * C];      // t_begin is 0 here: the old tail as it is
+        }
+    }
+    const float b = bias ? bias[c] : 0.0f;
+    for (int t = t_begin; t < t_end; t++) {
+        const float x = proj[(size_t)(row0 + t) * stride + conv_at + c];
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < SSD_MAX_TAPS - 1; j++)
+            if (j < past) acc = fmaf(w[j], hist[j], acc);
+        acc = fmaf(w[past], x, acc);
+#pragma unroll
+        for (int j = 0; j < SSD_MAX_TAPS - 2; j++)
+            if (j + 1 < past) hist[j] = hist[j + 1];
+        if (past > 0) hist[past - 1] = x;
+        xbc[(size_t)(row0 + t) * C + c] = acc / (1.0f + expf(-acc));
+    }
+    if (tile == 0 && write_tail) {
+        // The new tail: the last `past` inputs of the sequence, of which the step may have brought fewer.
+#pragma unroll
+        for (int i = 0; i < SSD_MAX_TAPS - 1; i++) {
+            if (i < past) {
+                const int t = n_rows - past + i;
+                tl[(size_t)i * C] = t >= 0 ? proj[(size_t)(row0 + t) * stride + conv_at + c] : old[i + n_rows];
+            }
+        }
+    }
+}
+
+// weight_t: [taps, C] (tap by tap; the last is the current token's); bias: [C] or null; dt_bias, a_log: [H];
+// tail: [slots, taps - 1, C]; xbc: [rows, C]; dtda: [rows, 2 H].
+extern "C" int bc_ssd_prepare(const float* proj, int stride, int conv_at, int dt_at, const float* weight_t, const float* bias, const float* dt_bias,
+                              const float* a_log, float* tail, const int* seq_rows, const int* seq_slot, float* xbc, float* dtda, int seqs,
+                              int max_new, int C, int H, int taps, int n_slots, int write_tail, cudaStream_t s) {
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && C > 0 && H > 0, "ssd_prepare: bad sizes seqs=%d max_new=%d C=%d H=%d", seqs, max_new, C, H);
+    BC_CHECK_ARG(taps >= 1 && taps <= SSD_MAX_TAPS, "ssd_prepare: %d taps are outside 1 to %d", taps, SSD_MAX_TAPS);
+    if (seqs == 0 || max_new == 0) return BC_OK;
+    const int tiles = (max_new + SSD_TILE - 1) / SSD_TILE;
+    BC_CHECK_ARG(tiles <= 65535, "ssd_prepare: %d rows a sequence are too many", max_new);
+    dim3 grid((C + H + 127) / 128, tiles, seqs);
+    bc_launch(ssd_prepare_kernel, grid, dim3(128), 0, s, proj, stride, conv_at, dt_at, weight_t, bias, dt_bias, a_log, tail, seq_rows, seq_slot, xbc,
+              dtda, C, H, taps, n_slots, write_tail);
+    BC_LAUNCH_STATUS();
+}
+
+// --------------------------------------------------------------------------------- gla_decay
+// decay[r][c] = sigmoid(z)^(1/tau) with z = sum_i w2t[i][c] inner[r][i] + b[c], computed as exp(-softplus(-z) / tau)
+// so that no logarithm of a rounded sigmoid is taken.  One block a row; the inner vector is staged in shared memory.
+__global__ void __launch_bounds__(256)
+gla_decay_kernel(const float* __restrict__ proj, int stride, int inner_at, const float* __restrict__ w2t, const float* __restrict__ b,
+                 float* __restrict__ decay, int W, int rank, float inv_tau) {
+    extern __shared__ float inner[];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(proj);
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) inner[i] = proj[(size_t)r * stride + inner_at + i];
+    __syncthreads();
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float z = b[c];
+        for (int i = 0; i < rank; i++) z = fmaf(w2t[(size_t)i * W + c], inner[i], z);
+        const float m = -z;                                          // softplus(m) = max(m, 0) + log1p(exp(-|m|))
+        const float sp = fmaxf(m, 0.0f) + log1pf(expf(-fabsf(m)));
+        decay[(size_t)r * W + c] = expf(-sp * inv_tau);
+    }
+}
+
+// proj: [rows, stride] float with the inner projection's `rank` values at column inner_at; w2t: [rank, W]; b: [W]; decay: [rows, W].
+extern "C" int bc_gla_decay(const float* proj, int stride, int inner_at, const float* w2t, const float* b, float* decay, int rows, int W, int rank,
+                            float tau, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && W > 0 && rank > 0 && rank <= 8192 && tau > 0.0f, "gla_decay: bad sizes rows=%d W=%d rank=%d tau=%g", rows, W, rank, (double)tau);
+    if (rows == 0) return BC_OK;
+    bc_launch(gla_decay_kernel, dim3(rows), dim3(W >= 1024 ? 256 : 128), (size_t)rank * sizeof(float), s, proj, stride, inner_at, w2t, b, decay, W,
+              rank, 1.0f / tau);
+    BC_LAUNCH_STATUS();
+}
+
+// -------------------------------------------------------------------------------- gated_norm
+// y: [rows, W] float; gate: row r's at gate + r * g_stride; weight: `period` values, repeated over the row (period = W: one
+// a column; period = W / parts: shared by the parts).  Block (part, row): z = y (* silu(g) if gate_first); z over the root mean
+// square of the part, eps inside the root; times weight (times silu(g) if not gate_first); times factor.
+template <class T>
+__global__ void __launch_bounds__(256)
+gated_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int g_stride, const float* __restrict__ weight, int period,
+                  T* __restrict__ out, int W, int part, float eps, int gate_first, float factor) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(y); PDL_FRESH(gate);
+    const int r = blockIdx.y, c0 = blockIdx.x * part;
+    const float* yr = y + (size_t)r * W + c0;
+    const float* gr = gate + (size_t)r * g_stride + c0;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < part; c += blockDim.x) {
+        float z = yr[c];
+        if (gate_first) {
+            const float g = gr[c];
+            z *= g / (1.0f + expf(-g));
+        }
+        ss = fmaf(z, z, ss);
+    }
+    const float scale = factor / sqrtf(block_sum(ss, scratch) / (float)part + eps);
+    for (int c = threadIdx.x; c < part; c += blockDim.x) {
+        const float g = gr[c];
+        const float sg = g / (1.0f + expf(-g));
+        const float z = gate_first ? yr[c] * sg : yr[c];
+        const float o = z * scale * weight[(c0 + c) % period];
+        out[(size_t)r * W + c0 + c] = from_f32<T>(gate_first ? o : o * sg);
+    }
+}
+
+template <class T>
+static int gated_norm(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W, int parts,
+                      float eps, int gate_first, float factor, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && rows <= 2147483647 && W > 0 && parts > 0 && parts <= 65535 && W % parts == 0, "gated_norm: bad sizes rows=%d W=%d parts=%d", rows, W, parts);
+    BC_CHECK_ARG(period > 0 && (period == W || period == W / parts), "gated_norm: a weight of %d values fits neither the row nor a part", period);
+    if (rows == 0) return BC_OK;
+    const int part = W / parts;
+    const int threads = part >= 1024 ? 256 : part >= 256 ? 128 : part >= 64 ? 64 : 32;       // by the part's width alone
+    dim3 grid(parts, rows > 65535 ? 65535 : rows);
+    // More rows than a grid's second dimension holds go in turns.
+    for (int at = 0; at < rows; at += 65535) {
+        const int n = rows - at < 65535 ? rows - at : 65535;
+        bc_launch(gated_norm_kernel<T>, dim3(parts, n), dim3(threads), 0, s, y + (size_t)at * W, gate + (size_t)at * g_stride, g_stride, weight, period,
+                  (T*)out + (size_t)at * W, W, part, eps, gate_first, factor);
+    }
+    BC_LAUNCH_STATUS();
+}
+extern "C" int bc_gated_norm_f32(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W,
+                                 int parts, float eps, int gate_first, float factor, cudaStream_t s) {
+    return gated_norm<float>(y, gate, g_stride, weight, period, out, rows, W, parts, eps, gate_first, factor, s);
+}
+extern "C" int bc_gated_norm_bf16(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W,
+                                  int parts, float eps, int gate_first, float factor, cudaStream_t s) {
+    return gated_norm<bf16>(y, gate, g_stride, weight, period, out, rows, W, parts, eps, gate_first, factor, s);
+}

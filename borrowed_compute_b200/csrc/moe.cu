@@ -1,0 +1,343 @@
+// A feed-forward of many small gated experts of which every row uses a few.
+//
+//   route      z = W_router h in float; score s = sigmoid(z) (or softmax over the experts); the `top` largest scores of a
+//              row choose its experts (the lower index wins a tie); weights are the scores, as they are or divided by their sum
+//   count, offsets, fill
+//              rows sorted by expert: perm[j] = the (row, choice) pair at sorted place j, place[row * top + c] = its place,
+//              and a table of tiles of MOE_BM sorted rows that lie in one expert each
+//   gate_up    act[j] = silu(w g) * (w u) with g = W_gate^e x, u = W_up^e x, x the pair's row, w its weight: the weight
+//              multiplies the expert's input (weight_on_input), or act[j] = silu(g) * u and the weight waits for combine
+//   down       y[j] = W_down^e act[j] in float
+//   combine    residual[r] += sum over r's choices, in the order of choice, of y[place] (times the weight if it waited)
+//
+// Every sum of a row runs in an order that the sizes alone fix, and no two blocks add into one place: a row's result is the
+// same bits in any batch and at every repeat.  The products here run on the CUDA cores in float (the true 32-bit path, and
+// the checked twin of the tensor-core grouped product).
+#include "common.cuh"
+
+#define MOE_BM 32
+#define MOE_BN 64
+#define MOE_BK 16
+#define MOE_MAX_TOP 16
+
+// -------------------------------------------------------------------------------------- route
+template <class T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const int* __restrict__ row_slot, int* __restrict__ choice,
+                 float* __restrict__ weight, int E, int K, int top, int softmax, int renorm) {
+    extern __shared__ float score[];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(h);
+    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (row_slot != nullptr && row_slot[r] < 0) {           // a padding row takes no expert
+        for (int c = threadIdx.x; c < top; c += blockDim.x) {
+            choice[(size_t)r * top + c] = -1;
+            weight[(size_t)r * top + c] = 0.0f;
+        }
+        return;
+    }
+    const T* x = h + (size_t)r * K;
+    for (int e = warp; e < E; e += warps) {
+        const float* w = router + (size_t)e * K;
+        float z = 0.0f;
+        for (int k = lane; k < K; k += 32) z = fmaf(to_f32(x[k]), w[k], z);
+        z = warp_sum(z);
+        if (lane == 0) score[e] = z == z ? z : -INFINITY;      // a row of not-a-numbers still chooses experts that exist
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // Scores from logits; the order of the experts is the order of their logits under either rule.
+    float zmax = -INFINITY;
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, score[e]);
+    zmax = warp_max(zmax);
+    float total = 0.0f;
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) total += expf(score[e] - zmax);
+        total = warp_sum(total);
+    }
+    float picked_sum = 0.0f, mine = 0.0f;
+    int mine_e = -1;
+    for (int c = 0; c < top; c++) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float z = score[e];
+            if (z != INFINITY && (best_e == 0x7fffffff || z > best)) { best = z; best_e = e; }     // taken ones are marked +inf
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) best_e = 0;
+        const float s = softmax ? expf(best - zmax) / total : 1.0f / (1.0f + expf(-best));
+        picked_sum += s;
+        if (lane == c % 32 && c / 32 == 0) { mine = s; mine_e = best_e; }
+        __syncwarp();
+        if (lane == 0) score[best_e] = INFINITY;
+        __syncwarp();
+    }
+    if (lane < top) {
+        choice[(size_t)r * top + lane] = mine_e;
+        weight[(size_t)r * top + lane] = renorm ? mine / picked_sum : mine;
+    }
+}
+
+// ------------------------------------------------------------------------- sorting by expert
+// One block an expert walks all (row, choice) pairs in order and counts its own.
+__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ choice, int pairs, int* __restrict__ counts) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(choice);
+    const int e = blockIdx.x;
+    int n = 0;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) n += choice[i] == e;
+    const float total = block_sum((float)n, scratch);        // exact: counts stay far below 2^24
+    if (threadIdx.x == 0) counts[e] = (int)total;
+}
+
+// One block: where every expert's rows start in sorted order, and the tiles.  table: [0] the number of tiles, then for tile t
+// at 1 + 3 t: expert, first sorted place, rows.
+__global__ void __launch_bounds__(32) moe_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ table,
+                                                        int max_tiles) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(counts);
+    if (threadIdx.x != 0) return;
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; e++) {
+        offsets[e] = at;
+        const int n = counts[e];
+        for (int s = 0; s < n && tiles < max_tiles; s += MOE_BM) {
+            table[1 + 3 * tiles] = e;
+            table[2 + 3 * tiles] = at + s;
+            table[3 + 3 * tiles] = min(MOE_BM, n - s);
+            tiles++;
+        }
+        at += n;
+    }
+    offsets[E] = at;
+    table[0] = tiles;
+}
+
+// One block an expert walks the pairs again, in the same order, and gives each of its own the next place.
+__global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ choice, int pairs, const int* __restrict__ offsets,
+                                                      int* __restrict__ perm, int* __restrict__ place) {
+    __shared__ int warp_counts[8];
+    __shared__ int base;
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(choice); PDL_FRESH(offsets);
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = offsets[e];
+    __syncthreads();
+    for (int i0 = 0; i0 < pairs; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        const bool hit = i < pairs && choice[i] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_counts[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0, all = 0;
+        for (int w = 0; w < 8; w++) {
+            if (w < warp) before += warp_counts[w];
+            all += warp_counts[w];
+        }
+        if (hit) {
+            const int j = base + before + __popc(ballot & ((1u << lane) - 1u));
+            perm[j] = i;
+            place[i] = j;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) base += all;
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------- grouped products
+template <class T>
+__device__ __forceinline__ void moe_load_tile(const T* __restrict__ src, const int* rows_of, int n_rows, int K, int k0, float (*smem)[MOE_BN + 4],
+                                              int tile_rows) {
+    // tile_rows x 16 values of a K-major matrix into smem[k][row]; rows_of (shared memory) names each row's source, -1: zeros.
+    for (int i = threadIdx.x; i < tile_rows * 4; i += blockDim.x) {
+        const int r = i >> 2, kq = (i & 3) * 4;
+        const int row = r < n_rows ? rows_of[r] : -1;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int k = k0 + kq + j;
+            smem[kq + j][r] = row >= 0 && k < K ? to_f32(src[(size_t)row * K + k]) : 0.0f;
+        }
+    }
+}
+
+// GATED: W is [E, 2 N, K] (gate rows, then up rows), out_act[j][n] = silu(w g) * (w u) with w = weight[perm[j]] if
+// weight_on_input else 1; X rows are gathered: sorted place j reads row perm[j] / top.
+// Not GATED: W is [E, N, K], X is [sorted places, K] as it lies, out_f32[j][n] = the sum.
+template <class T, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_product_kernel(const T* __restrict__ X, const T* __restrict__ W, const int* __restrict__ table, const int* __restrict__ perm,
+                   const float* __restrict__ weight, T* __restrict__ out_act, float* __restrict__ out_f32, int N, int K, int top,
+                   int weight_on_input) {
+    __shared__ float As[MOE_BK][MOE_BN + 4];       // only MOE_BM columns used
+    __shared__ float Bs[MOE_BK][MOE_BN + 4];
+    __shared__ float Cs[GATED ? MOE_BK : 1][MOE_BN + 4];
+    __shared__ int src_row[MOE_BM], w_row[MOE_BN];
+    __shared__ float row_w[MOE_BM];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(X); PDL_FRESH(table); PDL_FRESH(perm); PDL_FRESH(weight);
+    const int tile = blockIdx.y;
+    if (tile >= table[0]) return;
+    const int e = table[1 + 3 * tile], j0 = table[2 + 3 * tile], n_rows = table[3 + 3 * tile];
+    const int n0 = blockIdx.x * MOE_BN;
+    if (threadIdx.x < MOE_BM) {
+        const int j = j0 + threadIdx.x;
+        const bool in = threadIdx.x < n_rows;
+        src_row[threadIdx.x] = !in ? -1 : GATED ? perm[j] / top : j;
+        row_w[threadIdx.x] = in && GATED && weight_on_input ? weight[perm[j]] : 1.0f;
+    }
+    if (threadIdx.x < MOE_BN) w_row[threadIdx.x] = n0 + threadIdx.x < N ? n0 + threadIdx.x : -1;
+    __syncthreads();
+    const T* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;        // 16 x 8 threads, 4 x 4 outputs each
+    float acc[4][4] = {};
+    float acc2[GATED ? 4 : 1][4] = {};
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        moe_load_tile<T>(X, src_row, n_rows, K, k0, As, MOE_BM);
+        moe_load_tile<T>(We, w_row, MOE_BN, K, k0, Bs, MOE_BN);
+        if (GATED) moe_load_tile<T>(We + (size_t)N * K, w_row, MOE_BN, K, k0, Cs, MOE_BN);
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MOE_BK; k++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            if (GATED) {
+                float c[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) c[j] = Cs[k][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], c[j], acc2[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = ty * 4 + i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            const size_t o = (size_t)(j0 + r) * N + n;
+            if (GATED) {
+                const float g = acc[i][j] * row_w[r], u = acc2[GATED ? i : 0][j] * row_w[r];
+                out_act[o] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+            } else {
+                out_f32[o] = acc[i][j];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ combine
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ choice, const int* __restrict__ place, const float* __restrict__ weight,
+                   float* __restrict__ residual, int E, int top, int weight_on_output) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(y); PDL_FRESH(choice); PDL_FRESH(place); PDL_FRESH(weight);
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < E; c += blockDim.x) {
+        float sum = 0.0f;
+        bool any = false;
+        for (int i = 0; i < top; i++) {
+            if (choice[(size_t)r * top + i] < 0) continue;
+            const float v = y[(size_t)place[(size_t)r * top + i] * E + c];
+            sum = weight_on_output ? fmaf(weight[(size_t)r * top + i], v, sum) : sum + v;
+            any = true;
+        }
+        if (any) residual[(size_t)r * E + c] += sum;
+    }
+}
+
+// ------------------------------------------------------------------------------------ launchers
+template <class T>
+static int route(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top, int softmax,
+                 int renorm, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 8192, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
+    if (rows == 0) return BC_OK;
+    bc_launch(moe_route_kernel<T>, dim3(rows), dim3(128), (size_t)E * sizeof(float), s, (const T*)h, router, row_slot, choice, weight, E, K, top,
+              softmax, renorm);
+    BC_LAUNCH_STATUS();
+}
+// h: [rows, K] of the activation type; router: [E, K] float; row_slot: [rows] (negative: a padding row; may be null);
+// choice: [rows, top] int; weight: [rows, top] float.
+extern "C" int bc_moe_route_f32(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top,
+                                int softmax, int renorm, cudaStream_t s) {
+    return route<float>(h, router, row_slot, choice, weight, rows, E, K, top, softmax, renorm, s);
+}
+extern "C" int bc_moe_route_bf16(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top,
+                                 int softmax, int renorm, cudaStream_t s) {
+    return route<bf16>(h, router, row_slot, choice, weight, rows, E, K, top, softmax, renorm, s);
+}
+
+extern "C" int bc_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
+
+// choice: [pairs]; counts: [E]; offsets: [E + 1]; table: [1 + 3 * bc_moe_max_tiles(pairs, E)]; perm, place: [pairs].
+extern "C" int bc_moe_plan(const int* choice, int pairs, int E, int* counts, int* offsets, int* table, int* perm, int* place, cudaStream_t s) {
+    BC_CHECK_ARG(pairs >= 0 && E > 0 && E <= 65535, "moe_plan: bad sizes pairs=%d E=%d", pairs, E);
+    if (pairs == 0) return BC_OK;
+    bc_launch(moe_count_kernel, dim3(E), dim3(256), 0, s, choice, pairs, counts);
+    bc_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, E, offsets, table, bc_moe_max_tiles(pairs, E));
+    bc_launch(moe_fill_kernel, dim3(E), dim3(256), 0, s, choice, pairs, (const int*)offsets, perm, place);
+    BC_LAUNCH_STATUS();
+}
+
+template <class T>
+static int products(int gated, const void* X, const void* W, const int* table, const int* perm, const float* weight, void* out, int pairs, int E,
+                    int N, int K, int top, int weight_on_input, cudaStream_t s) {
+    BC_CHECK_ARG(pairs >= 0 && E > 0 && N > 0 && K > 0 && top > 0, "moe_product: bad sizes pairs=%d E=%d N=%d K=%d", pairs, E, N, K);
+    if (pairs == 0) return BC_OK;
+    const int tiles = bc_moe_max_tiles(pairs, E);
+    BC_CHECK_ARG(tiles <= 65535, "moe_product: %d tiles are too many", tiles);
+    dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
+    if (gated)
+        bc_launch(moe_product_kernel<T, true>, grid, dim3(128), 0, s, (const T*)X, (const T*)W, table, perm, weight, (T*)out, (float*)nullptr, N, K,
+                  top, weight_on_input);
+    else
+        bc_launch(moe_product_kernel<T, false>, grid, dim3(128), 0, s, (const T*)X, (const T*)W, table, perm, weight, (T*)nullptr, (float*)out, N, K,
+                  top, 0);
+    BC_LAUNCH_STATUS();
+}
+// gated: X [rows, K], W [E, 2 N, K], out [pairs, N] of the activation type; else X [pairs, K], W [E, N, K], out [pairs, N] float.
+extern "C" int bc_moe_product_f32(int gated, const void* X, const void* W, const int* table, const int* perm, const float* weight, void* out,
+                                  int pairs, int E, int N, int K, int top, int weight_on_input, cudaStream_t s) {
+    return products<float>(gated, X, W, table, perm, weight, out, pairs, E, N, K, top, weight_on_input, s);
+}
+extern "C" int bc_moe_product_bf16(int gated, const void* X, const void* W, const int* table, const int* perm, const float* weight, void* out,
+                                   int pairs, int E, int N, int K, int top, int weight_on_input, cudaStream_t s) {
+    return products<bf16>(gated, X, W, table, perm, weight, out, pairs, E, N, K, top, weight_on_input, s);
+}
+
+// y: [pairs, width] float in sorted order; residual: [rows, width] float.
+extern "C" int bc_moe_combine(const float* y, const int* choice, const int* place, const float* weight, float* residual, int rows, int width, int top,
+                              int weight_on_output, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && width > 0 && top > 0, "moe_combine: bad sizes rows=%d width=%d top=%d", rows, width, top);
+    if (rows == 0) return BC_OK;
+    bc_launch(moe_combine_kernel, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, s, y, choice, place, weight, residual, width, top, weight_on_output);
+    BC_LAUNCH_STATUS();
+}

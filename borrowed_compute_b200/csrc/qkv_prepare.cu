@@ -182,3 +182,103 @@ extern "C" int bc_qkv_prepare_bf16(const float* qkv, const float* bias, const fl
     return launch<bf16>(qkv, bias, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot, page_table, max_pages, n_pages, q_out, k_cache,
                         v_cache, rows, H, G, D, DV, rot, eps, normed, write_cache, s);
 }
+
+// ------------------------------------------------------------------------ norm a head
+// The same place in a layer for models that normalise every head of q and of k by itself: an RMS norm over
+// the head's D values with one weight of D values that all heads share (separately for q and for k), then
+// the rotation of the first `rot` dimensions, then q to the activation type and k, v into the cache.
+// `pairing` 0 pairs dimension i with i + rot/2, 1 pairs 2i with 2i + 1.  One warp a (row, head): the lanes
+// take pairs of dimensions, so the sum of squares and the rotation need no second pass over memory; which
+// values a lane adds, and in which order, depends on the sizes alone.
+template <class T>
+__global__ void __launch_bounds__(256)
+qkv_prepare_heads_kernel(const float* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                         const float* __restrict__ cos_sin, int n_positions, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                         const int* __restrict__ page_table, int max_pages, int n_pages, T* __restrict__ q_out, T* __restrict__ k_cache,
+                         T* __restrict__ v_cache, int H, int G, int D, int DV, int rot, int pairing, float eps, int normed, int write_cache) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(qkv);
+    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int nq = H * D, nk = G * D, nv = G * DV;
+    const float* x = qkv + (size_t)r * (nq + nk + nv);
+    const int slot = row_slot[r];
+    const int pos = row_pos[r];
+    const int half = rot / 2;
+    const bool turn = rot > 0 && cos_sin != nullptr && pos >= 0 && pos < n_positions;
+    const float* cs = cos_sin + (size_t)(turn ? pos : 0) * half * 2;
+    int page = -1;
+    if (slot >= 0 && pos >= 0 && pos / BC_PAGE < max_pages) page = page_table[(size_t)slot * max_pages + pos / BC_PAGE];
+    if (page >= n_pages) page = -1;
+    const bool cache = write_cache && page >= 0;
+    const int units = half + (D - rot);          // pairs that turn, then single dimensions that pass
+    for (int head = warp; head < H + G; head += warps) {
+        const bool is_q = head < H;
+        const float* xh = x + (size_t)head * D;      // keys follow the queries in the projection
+        const float* wt = is_q ? q_weight : k_weight;
+        float ss = 0.0f;
+        if (normed) {
+            for (int d = lane; d < D; d += 32) ss = fmaf(xh[d], xh[d], ss);
+            ss = warp_sum(ss);
+        }
+        const float scale = normed ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+        T* dst = is_q ? q_out + (size_t)r * nq + (size_t)head * D
+                      : k_cache + (((size_t)(cache ? page : 0) * G + (head - H)) * BC_PAGE + pos % BC_PAGE) * D;
+        if (!is_q && !cache) continue;
+        for (int u = lane; u < units; u += 32) {
+            if (u < half) {
+                const int a = pairing ? 2 * u : u, b = pairing ? 2 * u + 1 : u + half;
+                float va = xh[a] * (normed ? scale * wt[a] : 1.0f), vb = xh[b] * (normed ? scale * wt[b] : 1.0f);
+                if (turn) {
+                    const float c = cs[2 * u], s = cs[2 * u + 1];
+                    const float ra = va * c - vb * s, rb = vb * c + va * s;
+                    va = ra;
+                    vb = rb;
+                }
+                dst[a] = from_f32<T>(va);
+                dst[b] = from_f32<T>(vb);
+            } else {
+                const int d = rot + (u - half);
+                dst[d] = from_f32<T>(xh[d] * (normed ? scale * wt[d] : 1.0f));
+            }
+        }
+    }
+    if (cache) {
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            const int g = i / DV, d = i - g * DV;
+            v_cache[(((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * DV + d] = from_f32<T>(x[nq + nk + i]);
+        }
+    }
+}
+
+template <class T>
+static int launch_heads(const float* qkv, const float* q_weight, const float* k_weight, const float* cos_sin, int n_positions, const int* row_pos,
+                        const int* row_slot, const int* page_table, int max_pages, int n_pages, void* q_out, void* k_cache, void* v_cache, int rows,
+                        int H, int G, int D, int DV, int rot, int pairing, float eps, int normed, int write_cache, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && H > 0 && G > 0 && D > 0 && DV > 0, "qkv_prepare_heads: bad sizes rows=%d H=%d G=%d D=%d DV=%d", rows, H, G, D, DV);
+    BC_CHECK_ARG(rot >= 0 && rot % 2 == 0 && rot <= D, "qkv_prepare_heads: %d rotated dimensions of a head of %d", rot, D);
+    BC_CHECK_ARG(!normed || (q_weight && k_weight), "qkv_prepare_heads: the norm needs its weights");
+    if (rows == 0) return BC_OK;
+    const int heads = H + G;
+    const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;      // by the row's heads alone
+    bc_launch(qkv_prepare_heads_kernel<T>, dim3(rows), dim3(threads), 0, s, qkv, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot,
+              page_table, max_pages, n_pages, (T*)q_out, (T*)k_cache, (T*)v_cache, H, G, D, DV, rot, pairing, eps, normed, write_cache);
+    BC_LAUNCH_STATUS();
+}
+
+// As bc_qkv_prepare_*, without biases; q_weight and k_weight hold D values each; cos_sin: [n_positions, rot / 2, 2].
+extern "C" int bc_qkv_prepare_heads_f32(const float* qkv, const float* q_weight, const float* k_weight, const float* cos_sin, int n_positions,
+                                        const int* row_pos, const int* row_slot, const int* page_table, int max_pages, int n_pages, void* q_out,
+                                        void* k_cache, void* v_cache, int rows, int H, int G, int D, int DV, int rot, int pairing, float eps,
+                                        int normed, int write_cache, cudaStream_t s) {
+    return launch_heads<float>(qkv, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot, page_table, max_pages, n_pages, q_out, k_cache,
+                               v_cache, rows, H, G, D, DV, rot, pairing, eps, normed, write_cache, s);
+}
+extern "C" int bc_qkv_prepare_heads_bf16(const float* qkv, const float* q_weight, const float* k_weight, const float* cos_sin, int n_positions,
+                                         const int* row_pos, const int* row_slot, const int* page_table, int max_pages, int n_pages, void* q_out,
+                                         void* k_cache, void* v_cache, int rows, int H, int G, int D, int DV, int rot, int pairing, float eps,
+                                         int normed, int write_cache, cudaStream_t s) {
+    return launch_heads<bf16>(qkv, q_weight, k_weight, cos_sin, n_positions, row_pos, row_slot, page_table, max_pages, n_pages, q_out, k_cache,
+                              v_cache, rows, H, G, D, DV, rot, pairing, eps, normed, write_cache, s);
+}

@@ -5,11 +5,11 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------ embedding
-// out[r, :] = table[tokens[r], :] widened to float (the residual stream is float).
+// out[r, :] = table[tokens[r], :] * scale, widened to float (the residual stream is float); a scale of 1 changes nothing.
 // Reference: Part::embed, crates/bc-infer/src/model.rs:270-280.  A token outside the
 // table (the host rejects those before launch) yields a row of zeros, never a wild read.
 template <class T>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out, int E, int V) {
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out, int E, int V, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
@@ -30,11 +30,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
                                     __uint_as_float(raw.y & 0xffff0000u));
                 }
             }
-            *reinterpret_cast<float4*>(dst + c) = v;
+            *reinterpret_cast<float4*>(dst + c) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
         }
         return;
     }
-    for (int c = threadIdx.x; c < E; c += blockDim.x) dst[c] = ok ? to_f32(src[c]) : 0.0f;
+    for (int c = threadIdx.x; c < E; c += blockDim.x) dst[c] = ok ? to_f32(src[c]) * scale : 0.0f;
 }
 
 // -------------------------------------------------------------------------------- RMSNorm
@@ -338,10 +338,10 @@ static int pick_threads(int n, int cap = 256) {
 }
 
 #define ROWWISE_LAUNCHERS(SUFFIX, T)                                                                                             \
-    extern "C" int bc_embed_##SUFFIX(const void* table, const int* tokens, float* out, int rows, int E, int V, cudaStream_t s) { \
+    extern "C" int bc_embed_##SUFFIX(const void* table, const int* tokens, float* out, int rows, int E, int V, float scale, cudaStream_t s) { \
         BC_CHECK_ARG(rows >= 0 && E > 0 && V > 0, "embed: bad sizes rows=%d E=%d V=%d", rows, E, V);                             \
         if (rows == 0) return BC_OK;                                                                                             \
-        bc_launch(embed_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, (const T*)table, tokens, out, E, V);                                    \
+        bc_launch(embed_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, (const T*)table, tokens, out, E, V, scale);                                    \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_rmsnorm_##SUFFIX(const float* x, const float* w, void* out, const int* gather, int rows, int E, float eps, \

@@ -10,7 +10,7 @@ import torch
 
 from ..architectures import resolve
 from ..parts import base as P
-from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITION_ENCODINGS, CacheNeed, ModelSpec, PartSpec, Runtime, StateNeed,
+from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, JUNCTIONS, NORMS, POSITION_ENCODINGS, CacheNeed, ModelSpec, PartSpec, Runtime, StateNeed,
                           StepContext, TensorSpec)
 
 
@@ -29,6 +29,10 @@ class DecoderModel:
         self.embedding = _build(EMBEDDINGS, spec.embedding)
         self.position = None if spec.position is None else _build(POSITION_ENCODINGS, spec.position)
         self.blocks = [BLOCKS.get(layer.block).build(layer, spec.hidden_size) for layer in spec.layers]
+        self.junctions = [_build(JUNCTIONS, j) for j in spec.junctions]
+        for i, run in enumerate(spec.schedule):
+            if run.enter is not None and not 0 <= run.enter[0] < len(self.junctions):
+                raise ValueError(f"schedule entry {i} enters junction {run.enter[0]}, the model has {len(self.junctions)}")
         self.final_norm = _build(NORMS, spec.final_norm)
         self.head = _build(HEADS, spec.head)
         self.rt: Optional[Runtime] = None
@@ -40,6 +44,8 @@ class DecoderModel:
             yield self.spec.position.prefix, self.position
         for layer, block in zip(self.spec.layers, self.blocks):
             yield from block.named_parts(layer)
+        for spec, junction in zip(self.spec.junctions, self.junctions):
+            yield spec.prefix, junction
         yield self.spec.final_norm.prefix, self.final_norm
         yield self.spec.head.prefix, self.head
 
@@ -78,7 +84,14 @@ class DecoderModel:
         self.embedding.forward(ctx, residual)
         if self.position is not None:
             self.position.on_embeddings(residual, ctx)
+        embedded = None
+        if any(j.needs_embedding for j in self.junctions):
+            # The embedding's output is read again later: a second gather keeps it (the stream itself moves on).
+            embedded = torch.empty_like(residual)
+            self.embedding.forward(ctx, embedded)
         for i, run in enumerate(self.spec.schedule):
+            if run.enter is not None:
+                self.junctions[run.enter[0]].forward(residual, embedded, ctx, run.enter[1])
             self.blocks[run.layer].forward(residual, ctx, cache.memory(i), rt)
         h = torch.empty((n_want, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)
         self.final_norm.forward(residual, h, want_rows)

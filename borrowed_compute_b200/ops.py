@@ -132,7 +132,7 @@ def _bounds_paged(who: str, rows: int, row_pos: torch.Tensor, row_slot: torch.Te
 
 
 launches = 0   # kernels launched through this module since import (a captured graph replays them uncounted)
-_KERNELS_PER_CALL = {"bc_argmax": 2}   # launchers that start more than one kernel
+_KERNELS_PER_CALL = {"bc_argmax": 2, "bc_moe_plan": 3}   # launchers that start more than one kernel
 
 
 # Timing of single launches, for engine.profile.StepProfile: while `timeline` is a list every
@@ -144,6 +144,8 @@ _CLASS_OF = {
     "bc_embed": "embedding", "bc_rmsnorm": "norm", "bc_swiglu": "activation", "bc_rope_append": "rotary + append",
     "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
     "bc_short_conv": "short convolution", "bc_norm_pair": "norm", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
+    "bc_linear_scan": "recurrence", "bc_ssd_prepare": "recurrence set-up", "bc_gla_decay": "recurrence set-up", "bc_gated_norm": "gated norm",
+    "bc_moe_product": "expert product", "bc_moe": "routing", "bc_softcap": "softcap", "bc_reentry": "re-entry",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
 }
 
@@ -181,8 +183,8 @@ def _fn(name: str):
 
 # ---------------------------------------------------------------------------------- row-wise
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, :] = table[tokens[r], :] widened to float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[r, :] = table[tokens[r], :] * scale, widened to float32."""
     _need(table, "table")
     _need(tokens, "tokens", torch.int32)
     _need(out, "out", torch.float32)
@@ -190,7 +192,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
     if out.shape != (rows, E):
         raise KernelError(f"embed: out is {tuple(out.shape)}, wanted {(rows, E)}")
     _bounds("embed: tokens", tokens, V)
-    _call(_fn("bc_embed_" + _suffix(table.dtype)), _ptr(table), _ptr(tokens), _ptr(out), _c_int(rows), _c_int(E), _c_int(V), _stream())
+    _call(_fn("bc_embed_" + _suffix(table.dtype)), _ptr(table), _ptr(tokens), _ptr(out), _c_int(rows), _c_int(E), _c_int(V), _c_float(scale), _stream())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, gather: Optional[torch.Tensor] = None) -> None:
@@ -513,8 +515,10 @@ def attention_prefill_tc_status(reset: bool = True) -> int:
 
 def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                    row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
-                   window: int = 0, scale: Optional[float] = None, value_dim: Optional[int] = None, chunk: int = 0) -> None:
+                   window: int = 0, scale: Optional[float] = None, value_dim: Optional[int] = None, chunk: int = 0, sink: bool = False,
+                   out_scale: float = 1.0) -> None:
     """Causal attention of every row against its slot's cached positions, one warp a (row, head).
+    ``sink`` adds one to the softmax's denominator (a position of score 0 without a value); ``out_scale`` multiplies the result.
     ``value_dim`` (default: ``head_dim``) is the width of a head's values, ``chunk`` > 0 lets a
     position see only those of its own chunk of that many positions, counted from position 0."""
     _need(q, "q")
@@ -534,9 +538,10 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
     _bounds_paged("attention_rows", rows, row_pos, row_slot, page_table, k_cache.shape[0])
-    _call(_fn("bc_attention_rows_kv_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+    _call(_fn("bc_attention_rows_sink_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
           _ptr(row_pos), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim),
-          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _c_int(1 if sink else 0),
+          _c_float(out_scale), _stream())
 
 
 # ------------------------------------------------------- parts of other mixers and feed-forwards
@@ -726,6 +731,240 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optio
           _c_int(0 if q_weight is None else 1), _c_int(1 if write_cache else 0), _stream())
 
 
+def qkv_prepare_heads(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                      row_pos: torch.Tensor, row_slot: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, heads: int, kv_heads: int, head_dim: int, value_dim: int, rot_dims: int, pairing: int, eps: float,
+                      write_cache: bool = True) -> None:
+    """Between the fused projection (float32) and attention for models that normalise every head by itself: an RMS norm of each
+    head of q and of k over its ``head_dim`` values with weights of that many values shared by the heads (when given), rotation of
+    the first ``rot_dims`` dimensions of each head (``pairing`` 0: i with i + rot_dims/2; 1: 2i with 2i + 1), q into ``q_out`` and
+    k, v into the rows' places in the paged cache."""
+    _need(qkv, "qkv", torch.float32)
+    _need(q_out, "q_out")
+    _need(k_cache, "k_cache", q_out.dtype)
+    _need(v_cache, "v_cache", q_out.dtype)
+    _need(row_pos, "row_pos", torch.int32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(page_table, "page_table", torch.int32)
+    rows = qkv.shape[0]
+    nq, nk, nv = heads * head_dim, kv_heads * head_dim, kv_heads * value_dim
+    if qkv.shape[1] != nq + nk + nv or tuple(q_out.shape) != (rows, nq):
+        raise KernelError(f"qkv_prepare_heads: qkv {tuple(qkv.shape)} or q_out {tuple(q_out.shape)} do not fit the head sizes")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], kv_heads, PAGE, value_dim):
+        raise KernelError(f"qkv_prepare_heads: cache is {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qkv_prepare_heads: the norm needs both weights or none")
+    for t, name in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != head_dim:
+                raise KernelError(f"qkv_prepare_heads: {name} has {t.numel()} values, a head has {head_dim}")
+    n_positions = 0
+    if cos_sin is not None and rot_dims > 0:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape[1] != rot_dims // 2:
+            raise KernelError(f"qkv_prepare_heads: the rotary table has {cos_sin.shape[1]} pairs, {rot_dims} rotated dimensions want {rot_dims // 2}")
+        n_positions = cos_sin.shape[0]
+        _bounds("qkv_prepare_heads: row_pos", row_pos, n_positions, rows)
+    _bounds_paged("qkv_prepare_heads", rows, row_pos, row_slot, page_table, k_cache.shape[0])
+    _call(_fn("bc_qkv_prepare_heads_" + _suffix(q_out.dtype)), _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin if n_positions else None),
+          _c_int(n_positions), _ptr(row_pos), _ptr(row_slot), _ptr(page_table), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]),
+          _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim),
+          _c_int(rot_dims if n_positions else 0), _c_int(pairing), _c_float(eps), _c_int(0 if q_weight is None else 1),
+          _c_int(1 if write_cache else 0), _stream())
+
+
+# ----------------------------------------------------------- recurrences with a decaying outer-product state
+
+def linear_scan(q: torch.Tensor, q_at: int, q_rep: int, k: torch.Tensor, k_at: int, k_rep: int, v: torch.Tensor, v_at: int,
+                decay: torch.Tensor, decay_at: int, vector_decay: bool, kscale: Optional[torch.Tensor], kscale_at: int,
+                skip: Optional[torch.Tensor], out_scale: float, state: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
+                out: torch.Tensor, seqs: int, heads: int, key_dim: int, value_dim: int, write_state: bool = True) -> None:
+    """S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T, o_t = out_scale * S_t^T q_t + skip * v_t for every head over every sequence's rows
+    in time order, all float32.  q, k, v, decay and kscale are [rows, anything] tensors read from column ``*_at`` on: q and k hold
+    ``key_dim`` values for each group of ``*_rep`` heads, v ``value_dim`` a head, decay ``key_dim`` a head (``vector_decay``) or one,
+    kscale one a head (None: 1).  ``state`` [slots, heads, value_dim, key_dim] (value channel by value channel), ``out`` [rows, heads * value_dim]."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (decay, "decay"), (state, "state"), (out, "out")):
+        _need(t, name, torch.float32)
+    _need(seq_rows, "seq_rows", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    H, N, P = heads, key_dim, value_dim
+    rows = out.shape[0]
+    if tuple(state.shape[1:]) != (H, P, N) or out.shape[1] != H * P or H % q_rep or H % k_rep:
+        raise KernelError(f"linear_scan: state {tuple(state.shape)} or out {tuple(out.shape)} do not fit {H} heads of {N} x {P}")
+    for t, at, width, name in ((q, q_at, H // q_rep * N, "q"), (k, k_at, H // k_rep * N, "k"), (v, v_at, H * P, "v"),
+                               (decay, decay_at, H * N if vector_decay else H, "decay")):
+        if t.dim() != 2 or t.shape[0] < rows or at < 0 or at + width > t.shape[1]:
+            raise KernelError(f"linear_scan: {name} {tuple(t.shape)} has no {width} columns from {at} on for {rows} rows")
+    if kscale is not None:
+        _need(kscale, "kscale", torch.float32)
+        if kscale.dim() != 2 or kscale.shape[0] < rows or kscale_at + H > kscale.shape[1]:
+            raise KernelError(f"linear_scan: kscale {tuple(kscale.shape)} has no {H} columns from {kscale_at} on")
+    if skip is not None:
+        _need(skip, "skip", torch.float32)
+        if skip.numel() != H:
+            raise KernelError(f"linear_scan: skip has {skip.numel()} values for {H} heads")
+    _bounds("linear_scan: seq_slot", seq_slot, state.shape[0], seqs, lowest=-1)
+    _bounds("linear_scan: seq_rows", seq_rows, rows + 1, seqs + 1)
+
+    def at(t, col):
+        return _c_void_p(t.data_ptr() + 4 * col)
+
+    _call(_fn("bc_linear_scan"), at(q, q_at), _c_int(q.shape[1]), _c_int(q_rep), at(k, k_at), _c_int(k.shape[1]), _c_int(k_rep), at(v, v_at),
+          _c_int(v.shape[1]), at(decay, decay_at), _c_int(decay.shape[1]), _c_int(1 if vector_decay else 0),
+          _c_void_p(0) if kscale is None else at(kscale, kscale_at), _c_int(0 if kscale is None else kscale.shape[1]), _ptr(skip),
+          _c_float(out_scale), _ptr(state), _ptr(seq_rows), _ptr(seq_slot), _ptr(out), _c_int(seqs), _c_int(H), _c_int(N), _c_int(P),
+          _c_int(state.shape[0]), _c_int(1 if write_state else 0), _stream())
+
+
+SSD_MAX_TAPS = 9
+
+
+def ssd_prepare(proj: torch.Tensor, conv_at: int, dt_at: int, weight_t: torch.Tensor, bias: Optional[torch.Tensor], dt_bias: torch.Tensor,
+                a_log: torch.Tensor, tail: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor, xbc: torch.Tensor, dtda: torch.Tensor,
+                seqs: int, max_new: int, write_tail: bool = True) -> None:
+    """xbc = silu(bias + causal convolution over time of proj's columns conv_at ..), channel by channel, with ``weight_t`` [taps, C]
+    (the last tap is the current token's) and every slot's last taps - 1 inputs in ``tail`` [slots, taps - 1, C], brought up to date;
+    dtda[r] = (softplus(dt + dt_bias), exp(-exp(a_log) * that)) for the H step sizes at proj's columns dt_at ...  All float32."""
+    for t, name in ((proj, "proj"), (weight_t, "weight_t"), (dt_bias, "dt_bias"), (a_log, "a_log"), (tail, "tail"), (xbc, "xbc"), (dtda, "dtda")):
+        _need(t, name, torch.float32)
+    _need(seq_rows, "seq_rows", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    taps, C = weight_t.shape
+    H = dt_bias.numel()
+    rows = proj.shape[0]
+    if a_log.numel() != H or tuple(xbc.shape) != (rows, C) or tuple(dtda.shape) != (rows, 2 * H) or conv_at + C > proj.shape[1] or dt_at + H > proj.shape[1]:
+        raise KernelError(f"ssd_prepare: proj {tuple(proj.shape)}, xbc {tuple(xbc.shape)}, dtda {tuple(dtda.shape)} do not fit {C} channels and {H} heads")
+    if tuple(tail.shape[1:]) != (max(taps - 1, 1), C) or not 1 <= taps <= SSD_MAX_TAPS:
+        raise KernelError(f"ssd_prepare: tail {tuple(tail.shape)} does not fit {taps} taps of {C} channels (at most {SSD_MAX_TAPS} taps)")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != C:
+            raise KernelError(f"ssd_prepare: bias has {bias.numel()} values for {C} channels")
+    _bounds("ssd_prepare: seq_slot", seq_slot, tail.shape[0], seqs, lowest=-1)
+    _bounds("ssd_prepare: seq_rows", seq_rows, rows + 1, seqs + 1)
+    _call(_fn("bc_ssd_prepare"), _ptr(proj), _c_int(proj.shape[1]), _c_int(conv_at), _c_int(dt_at), _ptr(weight_t), _ptr(bias), _ptr(dt_bias),
+          _ptr(a_log), _ptr(tail), _ptr(seq_rows), _ptr(seq_slot), _ptr(xbc), _ptr(dtda), _c_int(seqs), _c_int(max_new), _c_int(C), _c_int(H),
+          _c_int(taps), _c_int(tail.shape[0]), _c_int(1 if write_tail else 0), _stream())
+
+
+def gla_decay(proj: torch.Tensor, inner_at: int, w2t: torch.Tensor, bias: torch.Tensor, decay: torch.Tensor, tau: float) -> None:
+    """decay = sigmoid(z)^(1/tau) with z = inner @ w2t + bias, inner being proj's columns inner_at .. inner_at + rank; float32."""
+    for t, name in ((proj, "proj"), (w2t, "w2t"), (bias, "bias"), (decay, "decay")):
+        _need(t, name, torch.float32)
+    rank, W = w2t.shape
+    rows = proj.shape[0]
+    if bias.numel() != W or tuple(decay.shape) != (rows, W) or inner_at + rank > proj.shape[1]:
+        raise KernelError(f"gla_decay: proj {tuple(proj.shape)}, w2t {tuple(w2t.shape)}, decay {tuple(decay.shape)} do not fit")
+    _call(_fn("bc_gla_decay"), _ptr(proj), _c_int(proj.shape[1]), _c_int(inner_at), _ptr(w2t), _ptr(bias), _ptr(decay), _c_int(rows), _c_int(W),
+          _c_int(rank), _c_float(tau), _stream())
+
+
+def gated_norm(y: torch.Tensor, gate: torch.Tensor, gate_at: int, weight: torch.Tensor, out: torch.Tensor, parts: int, eps: float,
+               gate_first: bool, factor: float = 1.0) -> None:
+    """Every row of y [rows, W] (float32) in ``parts`` equal parts, each divided by its own root mean square and multiplied by
+    ``weight`` (as wide as the row, or as a part and then shared by the parts); silu of the gate (columns gate_at .. of ``gate``,
+    float32) multiplies before the norm (``gate_first``) or after it; ``factor`` multiplies the result."""
+    _need(y, "y", torch.float32)
+    _need(gate, "gate", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    rows, W = y.shape
+    if out.shape != y.shape or gate.shape[0] < rows or gate_at + W > gate.shape[1] or W % parts or weight.numel() not in (W, W // parts):
+        raise KernelError(f"gated_norm: y {tuple(y.shape)}, gate {tuple(gate.shape)}, weight {weight.numel()}, {parts} parts do not fit")
+    _call(_fn("bc_gated_norm_" + _suffix(out.dtype)), _ptr(y), _c_void_p(gate.data_ptr() + 4 * gate_at), _c_int(gate.shape[1]), _ptr(weight),
+          _c_int(weight.numel()), _ptr(out), _c_int(rows), _c_int(W), _c_int(parts), _c_float(eps), _c_int(1 if gate_first else 0),
+          _c_float(factor), _stream())
+
+
+# ------------------------------------------------------------------------------ routed experts
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
+              softmax: bool = False, renorm: bool = False) -> None:
+    """choice [rows, top] (int32), weight [rows, top] (float32): every row's ``top`` experts by score, the lower index winning a tie.
+    Scores are sigmoid(router @ h) (or a softmax over the experts), computed in float32; weights are the chosen scores, divided by
+    their sum with ``renorm``.  Rows whose slot is negative choose nothing (-1)."""
+    _need(h, "h")
+    _need(router, "router", torch.float32)
+    _need(choice, "choice", torch.int32)
+    _need(weight, "weight", torch.float32)
+    rows, K = h.shape
+    E, top = router.shape[0], choice.shape[1]
+    if router.shape[1] != K or tuple(choice.shape) != (rows, top) or weight.shape != choice.shape:
+        raise KernelError(f"moe_route: h {tuple(h.shape)}, router {tuple(router.shape)}, choice {tuple(choice.shape)} do not fit")
+    if row_slot is not None:
+        _need(row_slot, "row_slot", torch.int32)
+    _call(_fn("bc_moe_route_" + _suffix(h.dtype)), _ptr(h), _ptr(router), _ptr(row_slot), _ptr(choice), _ptr(weight), _c_int(rows), _c_int(E),
+          _c_int(K), _c_int(top), _c_int(1 if softmax else 0), _c_int(1 if renorm else 0), _stream())
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    return int(_fn("bc_moe_max_tiles")(_c_int(pairs), _c_int(experts)))
+
+
+def moe_plan(choice: torch.Tensor, experts: int, counts: torch.Tensor, offsets: torch.Tensor, table: torch.Tensor, perm: torch.Tensor,
+             place: torch.Tensor) -> None:
+    """Sorts the (row, choice) pairs by expert: perm[j] names the pair at sorted place j, place[pair] its place; ``table`` lists tiles
+    of sorted rows that lie in one expert ([0]: how many; then expert, first place, rows for each)."""
+    for t, name in ((choice, "choice"), (counts, "counts"), (offsets, "offsets"), (table, "table"), (perm, "perm"), (place, "place")):
+        _need(t, name, torch.int32)
+    pairs = choice.numel()
+    if counts.numel() < experts or offsets.numel() < experts + 1 or table.numel() < 1 + 3 * moe_max_tiles(pairs, experts) or perm.numel() < pairs \
+            or place.numel() < pairs:
+        raise KernelError("moe_plan: a buffer is too small")
+    _call(_fn("bc_moe_plan"), _ptr(choice), _c_int(pairs), _c_int(experts), _ptr(counts), _ptr(offsets), _ptr(table), _ptr(perm), _ptr(place), _stream())
+
+
+def moe_product(gated: bool, x: torch.Tensor, w: torch.Tensor, table: torch.Tensor, perm: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                top: int, weight_on_input: bool = False) -> None:
+    """The experts' products over rows sorted by expert.  ``gated``: x [rows, K], w [E, 2 N, K] (gate rows, then up rows), out
+    [pairs, N] = silu(s g) * (s u) in x's type, s the pair's weight (1 unless ``weight_on_input``).  Else: x [pairs, K] in sorted
+    order, w [E, N, K], out [pairs, N] float32."""
+    _need(x, "x")
+    _need(w, "w", x.dtype)
+    _need(out, "out", x.dtype if gated else torch.float32)
+    E, n_w, K = w.shape
+    N = n_w // 2 if gated else n_w
+    pairs = out.shape[0]
+    if x.shape[1] != K or out.shape[1] != N or (not gated and x.shape[0] != pairs) or perm.numel() < pairs:
+        raise KernelError(f"moe_product: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    _call(_fn("bc_moe_product_" + _suffix(x.dtype)), _c_int(1 if gated else 0), _ptr(x), _ptr(w), _ptr(table), _ptr(perm), _ptr(weight), _ptr(out),
+          _c_int(pairs), _c_int(E), _c_int(N), _c_int(K), _c_int(top), _c_int(1 if weight_on_input else 0), _stream())
+
+
+def moe_combine(y: torch.Tensor, choice: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                weight_on_output: bool = False) -> None:
+    """residual[r] += the sum over row r's choices, in their order, of y[place of the pair] (times the pair's weight with ``weight_on_output``)."""
+    _need(y, "y", torch.float32)
+    _need(residual, "residual", torch.float32)
+    rows, top = choice.shape
+    if y.shape[1] != residual.shape[1] or residual.shape[0] < rows:
+        raise KernelError(f"moe_combine: y {tuple(y.shape)} and residual {tuple(residual.shape)} do not fit")
+    _call(_fn("bc_moe_combine"), _ptr(y), _ptr(choice), _ptr(place), _ptr(weight), _ptr(residual), _c_int(rows), _c_int(residual.shape[1]),
+          _c_int(top), _c_int(1 if weight_on_output else 0), _stream())
+
+
+# ----------------------------------------------------------------------- the stream and the scores
+
+def softcap(scores: torch.Tensor, cap: float) -> None:
+    """scores <- cap * tanh(scores / cap), in place; float32."""
+    _need(scores, "scores", torch.float32)
+    _call(_fn("bc_softcap_f32"), _ptr(scores), ctypes.c_longlong(scores.numel()), _c_float(cap), _stream())
+
+
+def reentry(x: torch.Tensor, x0: torch.Tensor, step: torch.Tensor, cat: torch.Tensor) -> None:
+    """cat[r] = [x[r]; x0[r]] in cat's type, then x[r] <- step: the operand of the product that mixes the stream with the
+    embedding's output, and the vector its epilogue adds onto."""
+    _need(x, "x", torch.float32)
+    _need(x0, "x0", torch.float32)
+    _need(step, "step", torch.float32)
+    _need(cat, "cat")
+    rows, E = x.shape
+    if x0.shape != x.shape or step.numel() != E or tuple(cat.shape) != (rows, 2 * E):
+        raise KernelError(f"reentry: x {tuple(x.shape)}, x0 {tuple(x0.shape)}, step {step.numel()}, cat {tuple(cat.shape)} do not fit")
+    _call(_fn("bc_reentry_" + _suffix(cat.dtype)), _ptr(x), _ptr(x0), _ptr(step), _ptr(cat), _c_int(rows), _c_int(E), _stream())
+
+
 _decode_scratch = {}
 
 
@@ -857,10 +1096,11 @@ def attention_tiles_accepts(heads: int, kv_heads: int, head_dim: int, value_dim:
 def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                     seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
                     heads: int, kv_heads: int, head_dim: int, value_dim: int, window: int = 0, chunk: int = 0,
-                    scale: Optional[float] = None) -> None:
+                    scale: Optional[float] = None, sink: bool = False, out_scale: float = 1.0) -> None:
     """Causal attention of every sequence's new rows (many, or one) against its cached positions on mma.sync
     tiles, bf16, with values of their own width, a sliding window and/or a chunk mask (``chunk`` > 0: a position
-    sees only those of its own chunk of that many positions, counted from position 0)."""
+    sees only those of its own chunk of that many positions, counted from position 0).  ``sink`` adds one to the
+    softmax's denominator (a position of score 0 without a value); ``out_scale`` multiplies the result."""
     for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (out, "out")):
         _need(t, name, torch.bfloat16)
     for t, name in ((page_table, "page_table"), (seq_rows, "seq_rows"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
@@ -874,9 +1114,10 @@ def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cac
     _bounds("attention_tiles: seq_slot", seq_slot, page_table.shape[0], seqs, lowest=-1)
     _bounds("attention_tiles: seq_rows", seq_rows, out.shape[0] + 1, seqs + 1)
     _bounds("attention_tiles: page_table", page_table, k_cache.shape[0], lowest=-1)
-    _call(_fn("bc_attention_prefill_kv_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
+    _call(_fn("bc_attention_prefill_sink_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-          _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale), _stream())
+          _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale),
+          _c_int(1 if sink else 0), _c_float(out_scale), _stream())
 
 
 def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0,

@@ -9,7 +9,9 @@ A model is put together from parts that know nothing of the model they are in:
 - a *position encoding* is a parameter of a mixer (rotary tables) or acts on embeddings;
 - a *short convolution* mixes a few neighbouring rows of one sequence on every channel and
   keeps the last of them as per-sequence state;
-- a *block* arranges norms, a mixer and a feed-forward around the residual stream.
+- a *block* arranges norms, a mixer and a feed-forward around the residual stream;
+- a *junction* acts on the residual stream between two layers (where a stretch of layers is
+  entered again, say) and may read the embedding's output.
 
 Each kind has a registry from a name to a class.  A model's specification
 (:class:`ModelSpec`) names a kind and its parameters for every layer separately, plus the
@@ -63,6 +65,7 @@ FEED_FORWARDS = Registry("feed-forward")
 POSITION_ENCODINGS = Registry("position encoding")
 CONVOLUTIONS = Registry("short convolution")
 BLOCKS = Registry("block")
+JUNCTIONS = Registry("junction")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
 
@@ -101,10 +104,13 @@ class LayerSpec:
 class RunSpec:
     """One entry of the order in which layers run.  ``layer`` indexes ModelSpec.layers and
     may occur in several entries (shared weights).  ``memory_of`` names an earlier entry
-    whose cache and state this run reads instead of keeping its own."""
+    whose cache and state this run reads instead of keeping its own.  ``enter`` = (junction,
+    pass) runs ModelSpec.junctions[junction] on the stream right before this run, telling it
+    the number of the pass that starts here (a stretch of layers that runs several times)."""
 
     layer: int
     memory_of: Optional[int] = None
+    enter: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -125,6 +131,8 @@ class ModelSpec:
     # (name, shape) of tensors a folder may hold although no part reads them (the norm of a
     # branch that a layer leaves out, say): tolerated when present, never asked for.
     tolerated: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+    # Parts that act on the stream between layers; a RunSpec's ``enter`` names one.
+    junctions: Tuple[PartSpec, ...] = ()
 
 
 # -------------------------------------------------------------------------- declared tensors
@@ -303,6 +311,12 @@ class Mixer(Part):
     def state_need(self) -> Optional[StateNeed]:
         return None
 
+    def more_state_needs(self) -> Dict[str, StateNeed]:
+        """Further per-sequence state by a name of the mixer's choosing (the last inputs of a
+        convolution inside it, say); a run finds each in ``RunMemory.states["mixer." + name]``.
+        Like the block's other state it cannot be put back after a cut, save the cut to 0."""
+        return {}
+
     def rollback_state(self, state: torch.Tensor, slot: int, length: int) -> bool:
         """A sequence is cut back to ``length`` positions.  Token-indexed memory goes back
         by its length alone, but per-sequence state has already absorbed the positions that
@@ -332,6 +346,16 @@ class ShortConvolution(Part):
     def forward(self, h: torch.Tensor, out: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor], writes: bool = True) -> None:
         """out = conv(h) for the rows of the step, each sequence continuing from ``state``;
         rows of padding sequences (slot -1) change nothing that outlives the step."""
+        raise NotImplementedError
+
+
+class Junction(Part):
+    """Acts on the residual stream between two layers."""
+
+    needs_embedding = False     # whether forward wants the embedding's output of the step's rows
+
+    def forward(self, residual: torch.Tensor, embedded: Optional[torch.Tensor], ctx: StepContext, number: int) -> None:
+        """Changes residual[:rows] in place; ``number`` counts the passes that have entered here."""
         raise NotImplementedError
 
 
@@ -391,9 +415,11 @@ class Block(Part):
                 yield spec.parts[role].prefix, self.parts[role]
 
     def state_needs(self) -> Dict[str, StateNeed]:
-        """Per-sequence state that parts of this block other than its mixer want, by role;
+        """Per-sequence state that parts of this block other than its mixer want, by role,
+        and what the mixer wants beside its own state ("mixer." + the mixer's name for it);
         a run of the block finds each in ``RunMemory.states``."""
-        return {}
+        mixer = self.memory_part()
+        return {} if mixer is None else {"mixer." + name: need for name, need in mixer.more_state_needs().items()}
 
     def rollback_states(self, states: Mapping[str, torch.Tensor], slot: int, length: int) -> bool:
         """Like ``Mixer.rollback_state`` for the state of ``state_needs``: True if every one

@@ -5,7 +5,9 @@ The pre-norm residual block: x += mixer(norm1(x)); x += feed_forward(norm2(x))
 
 The parallel block: x += mixer(conv(norm1(x))) + feed_forward(norm2(x)), both branches reading
 the same x, the mixer's input first passing a short causal convolution over time whose last
-inputs are per-sequence state.  The feed-forward (and its norm) may be left out."""
+inputs are per-sequence state.  The feed-forward (and its norm) may be left out; a feed-forward
+without a norm of its own reads what the mixer reads, x += mixer(h) + feed_forward(h) with
+h = norm1(x)."""
 
 from __future__ import annotations
 
@@ -38,22 +40,27 @@ class ParallelBlock(Block):
 
     def __init__(self, parts, hidden_size: int):
         super().__init__(parts, hidden_size)
-        if (self.norm2 is None) != (self.feed_forward is None):
-            raise ValueError("a parallel block has a feed-forward and its norm, or neither")
+        if self.norm2 is not None and self.feed_forward is None:
+            raise ValueError("a parallel block has no second norm without a feed-forward")
+        if self.norm2 is None and self.feed_forward is not None and self.conv is not None:
+            raise ValueError("a feed-forward that shares the mixer's norm cannot follow a convolution of the mixer's input")
 
     def _one_statistic(self) -> bool:
         """Whether both norms are plain RMS norms with the same eps, so that they share the row's statistic."""
         return type(self.norm1) is RMSNorm and (self.norm2 is None or (type(self.norm2) is RMSNorm and self.norm2.eps == self.norm1.eps))
 
     def state_needs(self) -> Dict[str, StateNeed]:
+        needs = super().state_needs()
         need = None if self.conv is None else self.conv.state_need()
-        return {} if need is None else {"conv": need}
+        if need is not None:
+            needs["conv"] = need
+        return needs
 
     def forward(self, residual: torch.Tensor, ctx: StepContext, mem: RunMemory, rt: Runtime) -> None:
         rows = residual.shape[0]
         # Both branches read the stream as it is now, so both norms run before either adds to it.
         h = torch.empty((rows, self.hidden_size), dtype=rt.dtype, device=residual.device)
-        h2 = torch.empty_like(h) if self.feed_forward is not None else None
+        h2 = torch.empty_like(h) if self.norm2 is not None else None
         if self._one_statistic():
             # Two RMS norms of the same rows are one kernel; in a step of single rows the convolution rides in it too.
             conv = self.conv if self.conv is not None and ctx.decode and isinstance(self.conv, CausalConvResidual) else None
@@ -75,4 +82,4 @@ class ParallelBlock(Block):
             h = hc
         self.mixer.forward(h, residual, ctx, mem)
         if self.feed_forward is not None:
-            self.feed_forward.forward(h2, residual, ctx)
+            self.feed_forward.forward(h if h2 is None else h2, residual, ctx)

@@ -13,9 +13,11 @@ from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, StepContext, Tens
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab_size: int, hidden_size: int, tensor: str = "weight"):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor)
-        self.vocab_size, self.hidden_size, self.tensor = int(vocab_size), int(hidden_size), str(tensor)
+    """``scale`` multiplies every embedded row (1: as stored)."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, tensor: str = "weight", scale: float = 1.0):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor, scale=scale)
+        self.vocab_size, self.hidden_size, self.tensor, self.scale = int(vocab_size), int(hidden_size), str(tensor), float(scale)
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size))}
@@ -25,7 +27,7 @@ class TokenEmbedding(Embedding):
         self.weight = tensors[self.tensor].contiguous()
 
     def forward(self, ctx: StepContext, residual: torch.Tensor) -> None:
-        ops.embed(self.weight, ctx.tokens[: residual.shape[0]], residual)
+        ops.embed(self.weight, ctx.tokens[: residual.shape[0]], residual, self.scale)
 
     def table(self) -> Optional[torch.Tensor]:
         return self.weight
@@ -34,11 +36,13 @@ class TokenEmbedding(Embedding):
 @HEADS.register("linear_head")
 class LinearHead(Head):
     """Scores = x W^T in float32.  A tied head has no tensor of its own and multiplies by
-    the embedding table (model.rs:200); a folder that still stores one is tolerated."""
+    the embedding table (model.rs:200); a folder that still stores one is tolerated.
+    ``softcap`` > 0 bounds the scores: s <- softcap * tanh(s / softcap)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, tensor: str = "weight"):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied, tensor=tensor)
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, tensor: str = "weight", softcap: float = 0.0):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied, tensor=tensor, softcap=softcap)
         self.vocab_size, self.hidden_size, self.tied, self.tensor = int(vocab_size), int(hidden_size), bool(tied), str(tensor)
+        self.softcap = float(softcap)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -53,3 +57,5 @@ class LinearHead(Head):
         if w is None:
             raise RuntimeError("a tied head needs the embedding's table")
         products.linear(x, w, out, products.EPI_STORE_F32, "head product")
+        if self.softcap > 0.0:
+            ops.softcap(out, self.softcap)

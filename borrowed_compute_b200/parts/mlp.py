@@ -14,23 +14,25 @@ from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int):
-        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size)
+    """``gate``, ``up`` and ``down`` are the names the three matrices carry after the part's prefix."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, gate: str = "gate_proj.weight", up: str = "up_proj.weight",
+                 down: str = "down_proj.weight"):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, gate=gate, up=up, down=down)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.names = (str(gate), str(up), str(down))
 
     def tensors(self) -> Dict[str, TensorSpec]:
         e, f = self.hidden_size, self.intermediate_size
-        return {
-            "gate_proj.weight": TensorSpec((f, e)),
-            "up_proj.weight": TensorSpec((f, e)),
-            "down_proj.weight": TensorSpec((e, f)),
-        }
+        gate, up, down = self.names
+        return {gate: TensorSpec((f, e)), up: TensorSpec((f, e)), down: TensorSpec((e, f))}
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
+        gate, up, down = self.names
         # Gate rows stacked on up rows: the product's epilogue pairs row j with row F + j.
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+        self.w_down = tensors[down].contiguous()
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)

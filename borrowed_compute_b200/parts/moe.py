@@ -1,0 +1,74 @@
+"""A feed-forward of many small gated experts of which every row uses a few, plus (optionally) a shared expert
+that every row uses.
+
+Router scores are sigmoid(W_router h) (or a softmax over the experts) in float; the ``top`` largest choose a row's
+experts and are its weights, as they are or divided by their sum (``renormalize``).  The weight multiplies the
+expert's input (``weight_on="input"``: the sum over the chosen experts of expert(w h)) or its output.  An expert is
+down( silu(gate x) * (up x) ).
+
+Rows are sorted by expert on the device (nothing of a step's routing reaches the host, so a captured step replays),
+the experts' two products run over the sorted rows, and a last kernel adds every row's results in the order of its
+choices: no two blocks add into one place, so a row's result does not depend on the batch.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+
+from .. import ops
+from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, TensorSpec
+from .mlp import SwiGLU
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, experts: int, top: int, intermediate_size: int, shared_size: int = 0, score: str = "sigmoid",
+                 renormalize: bool = False, weight_on: str = "input"):
+        super().__init__(hidden_size=hidden_size, experts=experts, top=top, intermediate_size=intermediate_size, shared_size=shared_size,
+                         score=score, renormalize=renormalize, weight_on=weight_on)
+        self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
+        self.intermediate_size, self.shared_size = int(intermediate_size), int(shared_size)
+        if not 0 < self.top <= self.experts or self.top > 16:
+            raise ValueError(f"{top} of {experts} experts a row is outside what the router takes (1 to 16, at most all)")
+        if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError(f"score {score!r} must be 'sigmoid' or 'softmax', weight_on {weight_on!r} 'input' or 'output'")
+        self.softmax, self.renormalize, self.on_input = score == "softmax", bool(renormalize), weight_on == "input"
+        self.shared = SwiGLU(hidden_size, shared_size, gate="shared.gate", up="shared.up", down="shared.down") if self.shared_size > 0 else None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        e, f = self.hidden_size, self.intermediate_size
+        out = {"router": TensorSpec((self.experts, e), role="vector")}
+        for i in range(self.experts):
+            out.update({f"e{i}.gate": TensorSpec((f, e)), f"e{i}.up": TensorSpec((f, e)), f"e{i}.down": TensorSpec((e, f))})
+        if self.shared is not None:
+            out.update(self.shared.tensors())
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().load(tensors, rt)
+        self.router = tensors["router"].contiguous()
+        # [experts, 2 ff, width]: an expert's gate rows, then its up rows; [experts, width, ff].
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{i}.gate"], tensors[f"e{i}.up"]], dim=0) for i in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[f"e{i}.down"] for i in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.load({n: tensors[n] for n in self.shared.tensors()}, rt)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        rows, E, top, dev = x.shape[0], self.experts, self.top, x.device
+        pairs = rows * top
+        i32 = dict(dtype=torch.int32, device=dev)
+        choice = torch.empty((rows, top), **i32)
+        weight = torch.empty((rows, top), dtype=torch.float32, device=dev)
+        ops.moe_route(x, self.router, ctx.row_slot, choice, weight, softmax=self.softmax, renorm=self.renormalize)
+        ints = torch.empty(E + (E + 1) + (1 + 3 * ops.moe_max_tiles(pairs, E)) + 2 * pairs, **i32)
+        counts, offsets, table, perm, place = torch.split(ints, [E, E + 1, 1 + 3 * ops.moe_max_tiles(pairs, E), pairs, pairs])
+        ops.moe_plan(choice, E, counts, offsets, table, perm, place)
+        act = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=dev)
+        ops.moe_product(True, x, self.w_gate_up, table, perm, weight, act, top, weight_on_input=self.on_input)
+        y = torch.empty((pairs, self.hidden_size), dtype=torch.float32, device=dev)
+        ops.moe_product(False, act, self.w_down, table, perm, weight, y, top)
+        ops.moe_combine(y, choice, place, weight, residual, weight_on_output=not self.on_input)
+        if self.shared is not None:
+            self.shared.forward(x, residual, ctx)
