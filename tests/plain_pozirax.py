@@ -210,9 +210,17 @@ def route(h, router, top):
     return order, np.take_along_axis(s, order, axis=-1)
 
 
-def moe_feed_forward(h, w, p, mlp):
+def route_margin(h, router, top):
+    """The least distance, over the rows, between the last chosen expert's logit and the first one left out."""
+    z = np.sort(h @ router.T, axis=-1)[:, ::-1]
+    return float(np.min(z[:, top - 1] - z[:, top])) if top < z.shape[1] else math.inf
+
+
+def moe_feed_forward(h, w, p, mlp, stats=None):
     """The sum over a row's chosen experts of expert(weight * h), plus a shared expert of h."""
     chosen, weight = route(h, w[p + "router"], mlp["router"]["top"])
+    if stats is not None:
+        stats["margin"] = min(stats.get("margin", math.inf), route_margin(h, w[p + "router"], mlp["router"]["top"]))
     out = np.zeros((h.shape[0], w[p + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t], weight[t]):
@@ -236,8 +244,9 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(cfg, w, tokens, layers_out=None):
-    """Scores [T, vocab] of one whole sequence."""
+def forward(cfg, w, tokens, layers_out=None, stats=None):
+    """Scores [T, vocab] of one whole sequence.  `layers_out` (a list) receives the stream after every run of a
+    layer; `stats` (a dict) the least margin by which any router chose ("margin")."""
     w = {n: f64(a) for n, a in w.items()}
     eps = cfg["norm"]["eps"]
     x0 = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
@@ -253,13 +262,34 @@ def forward(cfg, w, tokens, layers_out=None):
             mixed = side_by_side_mixer(h, w, p + "mix.", layer["mixer"], eps)[0]
         else:
             raise ValueError(layer["type"])
-        ff = moe_feed_forward(h, w, p + "mlp.", layer["mlp"]) if layer.get("mlp") is not None else 0.0
+        ff = moe_feed_forward(h, w, p + "mlp.", layer["mlp"], stats) if layer.get("mlp") is not None else 0.0
         x = x + (mixed + ff)
-        if layer_runs is not None and layers_out is not None:
+        if layers_out is not None:
             layers_out.append(x.copy())
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     cap = cfg.get("logit_softcap")
     return cap * np.tanh(logits / cap) if cap else logits
+
+
+def generate(cfg, w, prompt, n):
+    """Greedy continuation (the lowest id among equal scores), recomputing the whole sequence a token."""
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(np.argmax(forward(cfg, w, seq)[-1])))
+    return seq[len(prompt):]
+
+
+def decisive_tokens(cfg, w, n, seed, margin=0.08):
+    """n random tokens for which every router of the model chooses by at least `margin` at every position, so that
+    rounding to bfloat16 cannot change a choice (a changed choice is another, equally valid, model output; a
+    comparison with this implementation would say nothing).  Seeds are tried in turn."""
+    for attempt in range(200):
+        toks = [int(t) for t in np.random.default_rng(1000 * seed + attempt).integers(0, cfg["vocab"], n)]
+        stats = {}
+        ref = forward(cfg, w, toks, stats=stats)
+        if stats.get("margin", math.inf) >= margin:
+            return toks, ref
+    raise RuntimeError("no decisive sequence found")
 
 
 # ------------------------------------------------------------------- small models for the tests
