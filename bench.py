@@ -521,25 +521,15 @@ def _against(costs, measured, pk, fp32_tflops):
     return out
 
 
-def bench_fegidra(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
-    """Prompt and decode throughput of a Fegidra model of ``layers`` layers at sizes that resemble a real model's
-    layers (random weights), beside a Llama model of the same width, heads, feed-forward width, vocabulary and
-    depth, and every kernel class of both against its own bytes or operations (eager steps, events around
-    every launch).  Inputs exceed the L2: a step reads hundreds of MB of weights."""
+def _bench_models(configs, costs_of, vocab, out, pk, rng, fp32_tflops, batch, prompt, steps, warmup):
+    """For each (name, config): decode steps of ``batch`` sequences after prompts of ``prompt`` tokens, one prompt alone,
+    all prompts in one step, and every kernel class launch by launch against ``costs_of(name, config)``."""
     import torch
 
     from borrowed_compute_b200.engine import Engine, StepEntry, StepProfile
 
-    c = FEGIDRA_SIZES[size]
-    # 128 float32 lanes an SM, one fused multiply-add a clock each, at the clock the part sustains (nominal 1.965 GHz)
-    fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
-    configs = {"fegidra": fegidra_config(layers=layers, **c),
-               "llama": llama_like(c["width"], c["heads"], c["kv_heads"], c["dim"], c["ff"], c["vocab"], layers)}
-    out = {"size": size, "sizes": c, "layers": layers, "batch": batch, "prompt": prompt,
-           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(fp32_tflops, 1)}
     for name, cfg in configs.items():
         eng = Engine.from_random(cfg, seed=1, max_tokens=batch * (prompt + 256), max_slots=batch, max_seq=prompt + 256)
-        vocab = c["vocab"]
         prompts = [[int(t) for t in rng.integers(0, vocab, prompt)] for _ in range(batch)]
         # the step of all prompts once untimed (a kernel's first launch loads it), then timed inside timed_decode
         warm = [eng.acquire() for _ in range(batch)]
@@ -581,7 +571,7 @@ def bench_fegidra(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=
         prefill_classes = prof.classes(1)
         eng.release(slot)
         eng.raise_on_kernel_error()
-        costs = fegidra_costs(c, layers, batch, prompt + 2, prompt) if name == "fegidra" else class_costs(cfg, layers, batch, batch * (prompt + 2), prompt)
+        costs = costs_of(name, cfg)
         out[name] = {
             "decode_ms_per_step": round(res["ms_per_step"], 4), "decode_tok_s": round(res["tok_s"], 1),
             "prompt_ms": round(prompt_ms, 3), "prompt_tok_s": round(prompt / (prompt_ms / 1000.0), 1),
@@ -594,6 +584,125 @@ def bench_fegidra(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=
         free_device_memory()
     return out
 
+
+# 128 float32 lanes an SM, one fused multiply-add a clock each, at the clock the part sustains (nominal 1.965 GHz)
+FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
+
+
+def bench_fegidra(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
+    """Prompt and decode throughput of a Fegidra model of ``layers`` layers at sizes that resemble a real model's
+    layers (random weights), beside a Llama model of the same width, heads, feed-forward width, vocabulary and
+    depth, and every kernel class of both against its own bytes or operations (eager steps, events around
+    every launch).  Inputs exceed the L2: a step reads hundreds of MB of weights."""
+    c = FEGIDRA_SIZES[size]
+    configs = {"fegidra": fegidra_config(layers=layers, **c),
+               "llama": llama_like(c["width"], c["heads"], c["kv_heads"], c["dim"], c["ff"], c["vocab"], layers)}
+    out = {"size": size, "sizes": c, "layers": layers, "batch": batch, "prompt": prompt,
+           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(FP32_TFLOPS, 1)}
+
+    def costs_of(name, cfg):
+        return fegidra_costs(c, layers, batch, prompt + 2, prompt) if name == "fegidra" else class_costs(cfg, layers, batch, batch * (prompt + 2), prompt)
+
+    return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
+
+
+# -------------------------------------------------------------------- the third architecture
+def pozirax_config(width, heads, kv_heads, dim, vdim, window, ssm_heads, ssm_vdim, state, groups, gla_heads, gla_dim, gla_vdim, rank, experts,
+                   top, ff, shared, vocab, layers):
+    """``layers`` layers of the Pozirax design: gated-linear-attention layers and layers of sliding-window attention beside a
+    state-space mixer in turn, each with routed experts and a shared expert."""
+    out = []
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": shared}}
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer, kind = {"heads": gla_heads, "dim": gla_dim, "vdim": gla_vdim, "tau": 16.0, "rank": rank}, "gla"
+        else:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "rot": {"dims": dim, "base": 1e6},
+                    "scale": 1.0 / dim ** 0.5}
+            right = {"heads": ssm_heads, "vdim": ssm_vdim, "state": state, "groups": groups, "norm_groups": groups, "conv": 4}
+            mixer, kind = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7}, "parallel"
+        out.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Pozirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+            "layers": out}
+
+
+POZIRAX_SIZES = {
+    # the width and attention heads of the 8B shape; 32 experts of 2,048 of which a row uses 4, and a shared expert of 4,096
+    "wide": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, ssm_heads=64, ssm_vdim=64, state=128, groups=8,
+                 gla_heads=16, gla_dim=128, gla_vdim=256, rank=16, experts=32, top=4, ff=2048, shared=4096, vocab=32000),
+    # a 2,048-wide model: 64 experts of 1,408 of which a row uses 6, and a shared expert of 2,816
+    "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=64, window=512, ssm_heads=32, ssm_vdim=64, state=64, groups=4,
+                gla_heads=8, gla_dim=128, gla_vdim=256, rank=16, experts=64, top=6, ff=1408, shared=2816, vocab=32000),
+}
+
+
+def pozirax_costs(c, layers, batch, ctx_len, T) -> dict:
+    """What each kernel class of the Pozirax model has to move in a decode step (bytes) and to compute in a prompt step of T
+    tokens (operations, or bytes where it only moves data), summed over the model's layers.  Even layers are gated linear
+    attention, odd ones attention beside a state-space mixer."""
+    E, H, G, D, DV, W, V = c["width"], c["heads"], c["kv_heads"], c["dim"], c["vdim"], c["window"], c["vocab"]
+    Hs, Ps, N, Gs = c["ssm_heads"], c["ssm_vdim"], c["state"], c["groups"]
+    Hg, Dg, Pg, rank = c["gla_heads"], c["gla_dim"], c["gla_vdim"], c["rank"]
+    X, k, f, fs = c["experts"], c["top"], c["ff"], c["shared"]
+    ng, np_, B = (layers + 1) // 2, layers // 2, batch
+    inner, conv = Hs * Ps, Hs * Ps + 2 * Gs * N
+    n_gla, n_ssm, n_qkv = 2 * Hg * Dg + 2 * Hg * Pg + rank, 2 * inner + 2 * Gs * N + Hs, H * D + G * D + G * DV
+    state_g, state_s = Hg * Dg * Pg * 4.0, Hs * N * Ps * 4.0
+    seen_decode = min(ctx_len + 1, W)
+    seen_prefill = sum(min(t + 1, W) for t in range(T))
+    touched = X * (1.0 - (1.0 - k / X) ** B)                          # experts that a step of B rows reads, on average
+    decode = {
+        "norm": (layers + 1) * (B * E * 6.0 + E * 4.0),
+        "recurrence projections": ng * (2.0 * n_gla * E + B * (2.0 * E + 4.0 * n_gla)) + np_ * (2.0 * n_ssm * E + B * (2.0 * E + 4.0 * n_ssm)),
+        "recurrence set-up": ng * (4.0 * rank * Hg * Dg + B * 4.0 * (rank + Hg * Dg)) + np_ * B * 4.0 * (2 * conv + 6 * conv + 3 * Hs),
+        "recurrence": ng * B * (2.0 * state_g + 4.0 * (3 * Hg * Dg + 2 * Hg * Pg)) + np_ * B * (2.0 * state_s + 4.0 * (2 * conv + 2 * Hs)),
+        "gated norm": (ng * Hg * Pg + np_ * inner) * B * 10.0,
+        "qkv product": np_ * (2.0 * n_qkv * E + B * (2.0 * E + 4.0 * n_qkv)),
+        "rotary + append": np_ * B * 6.0 * n_qkv,
+        "attention": np_ * B * (seen_decode * G * (D + DV) * 2.0 + 2.0 * H * (D + DV)),
+        "output product": ng * (2.0 * Hg * Pg * E + B * (2.0 * Hg * Pg + 8.0 * E)) + np_ * (2.0 * (H * DV + inner) * E + B * (2.0 * (H * DV + inner) + 16.0 * E)),
+        "routing": layers * (4.0 * X * E + B * (2.0 * E + 8.0 * k) + B * k * E * 4.0 + B * E * 8.0),
+        "expert product": layers * (touched * 3.0 * f * E * 2.0 + B * k * (2.0 * E + 4.0 * f + 4.0 * E)),
+        "gate/up product": layers * (4.0 * fs * E + B * (2.0 * E + 2.0 * fs)),
+        "down product": layers * (2.0 * fs * E + B * (2.0 * fs + 8.0 * E)),
+        "head product": 2.0 * V * E + B * (2.0 * E + 4.0 * V),
+    }
+    prefill = {
+        "norm": ("bytes", layers * T * E * 6.0),
+        "recurrence projections": ("flops", 2.0 * T * E * (ng * n_gla + np_ * n_ssm)),
+        "recurrence set-up": ("bytes", ng * T * 4.0 * (rank + Hg * Dg) + np_ * T * 4.0 * (2 * conv + 3 * Hs)),
+        # a step of the recurrence: the update and the output, two fused multiply-adds a state element
+        "recurrence": ("flops32", T * 4.0 * (ng * Hg * Dg * Pg + np_ * Hs * N * Ps)),
+        "gated norm": ("bytes", (ng * Hg * Pg + np_ * inner) * T * 10.0),
+        "qkv product": ("flops", np_ * 2.0 * T * n_qkv * E),
+        "rotary + append": ("bytes", np_ * T * 6.0 * n_qkv),
+        "attention": ("flops", np_ * 2.0 * H * (D + DV) * seen_prefill),
+        "output product": ("flops", 2.0 * T * E * (ng * Hg * Pg + np_ * (H * DV + inner))),
+        "routing": ("bytes", layers * T * (2.0 * E + 8.0 * k + k * E * 4.0 + E * 8.0)),
+        "expert product": ("flops", layers * 2.0 * T * k * 3.0 * f * E),
+        "gate/up product": ("flops", layers * 4.0 * T * fs * E),
+        "down product": ("flops", layers * 2.0 * T * fs * E),
+    }
+    return {"decode": decode, "prefill": prefill}
+
+
+def bench_pozirax(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
+    """Prompt and decode throughput of a Pozirax model of ``layers`` layers at sizes that resemble a real model's layers
+    (random weights), beside a Fegidra model, the closest of the other designs (recurrent and attention layers in turn,
+    parallel blocks), of the same width, attention heads, vocabulary and depth, whose dense feed-forward is as wide as the
+    experts a row uses; every kernel class of both against its own bytes or operations."""
+    c = POZIRAX_SIZES[size]
+    active = c["top"] * c["ff"] + c["shared"]
+    f = dict(width=c["width"], heads=c["heads"], kv_heads=c["kv_heads"], dim=c["dim"], vdim=c["vdim"], chunk=c["window"],
+             delta_heads=c["width"] // 64, delta_dim=64, rank=64, ff=active, vocab=c["vocab"])
+    configs = {"pozirax": pozirax_config(layers=layers, **c), "fegidra": fegidra_config(layers=layers, **f)}
+    out = {"size": size, "sizes": c, "beside": f, "layers": layers, "batch": batch, "prompt": prompt,
+           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(FP32_TFLOPS, 1)}
+
+    def costs_of(name, cfg):
+        return pozirax_costs(c, layers, batch, prompt + 2, prompt) if name == "pozirax" else fegidra_costs(f, layers, batch, prompt + 2, prompt)
+
+    return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
 
 
 def run_ours(args) -> dict:
@@ -754,9 +863,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
-    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra"],
+    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra", "pozirax"],
                     help="run one of the further workloads alone and print its figures (not the default run's one JSON line)")
-    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra: which sizes")
+    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra or pozirax: which sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "
@@ -773,7 +882,8 @@ def main() -> int:
         rng = np.random.default_rng(0)
         one = {"long": lambda: bench_long(peaks(), rng, args.layers), "13b": lambda: bench_13b(peaks(), rng), "3b": lambda: bench_3b(peaks(), rng),
                "tiny": lambda: bench_tiny(rng),
-               "fegidra": lambda: bench_fegidra(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
+               "fegidra": lambda: bench_fegidra(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
+               "pozirax": lambda: bench_pozirax(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
         print(json.dumps({"point": args.point, **one()}))
         return 0
     print(json.dumps(run_ours(args)))

@@ -941,6 +941,220 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     return BC_ERR_ARG;
 }
 
+// ------------------------------------------------------------ the product over groups of rows
+// Many weight matrices of one shape ([experts, rows, K], one after another) and activation rows sorted by the
+// matrix each of them meets: a table written on the device ([0]: tiles; then, a tile, matrix, first row, rows)
+// cuts the sorted rows into tiles that lie in one matrix each.  Block (x, y) multiplies weight tile x of the
+// matrix of table tile y with that tile's rows: the one-block kernel above without the splits, with its tile's
+// place read from the table.  The table comes from the kernels before, so nothing is asked for ahead of the
+// wait for them; the grid covers the most tiles the table can hold and blocks past its count leave at once.
+// A tile's box of rows may reach into the next matrix's rows (or past the last row, where TMA fills zeros):
+// those columns are computed and never written.
+struct TcGroupParams {
+    void* out;              // bf16 [rows, N] (SwiGLU) or float [rows, N]
+    const int* table;
+    int N, K;               // outputs a matrix and row, depth
+    int matrix_rows;        // weight rows a matrix: N, or 2 N for SwiGLU (gate rows, then up rows)
+    int stages;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(tc_threads(BN), 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcGroupParams p) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    constexpr int B_BYTES = BN * TC_BK * 2;
+    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = N_ACC * BN < 32 ? 32 : N_ACC * BN;
+    constexpr int HALVES = (tc_threads(BN) - 64) / 128;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * 16 + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int gave_up;
+
+    pdl_wait();                                   // the table, the rows and the output belong to the kernels before
+    const int* table = p.table;
+    PDL_FRESH(table);
+    const int tile = blockIdx.y;
+    if (tile >= table[0]) return;                 // the whole block, before anything is set up
+    const int matrix = table[1 + 3 * tile], t0 = table[2 + 3 * tile], t_count = table[3 + 3 * tile];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+    const int n0 = blockIdx.x * TC_BM;
+    const int w_row = matrix * p.matrix_rows + n0, w_row2 = w_row + p.N;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), acc_bar = smem_u32(&bars[32]);
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint64_t stream_once = l2_evict_first_policy();
+            for (int i = 0; i < k_iters; i++) {
+                const int s = i % stages;
+                if (i >= stages && !mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, 1)) {
+                    *reinterpret_cast<volatile int*>(&gave_up) = 1;
+                    break;
+                }
+                const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const int k = i * TC_BK;
+                if (BN <= 32) {                       // few rows a matrix: its weights are read once
+                    tma_load_2d_hint(a, &map_w, full0 + 8 * s, k, w_row, stream_once);
+                    if (N_ACC == 2) tma_load_2d_hint(a + A_BYTES, &map_w, full0 + 8 * s, k, w_row2, stream_once);
+                } else {
+                    tma_load_2d(a, &map_w, full0 + 8 * s, k, w_row);
+                    if (N_ACC == 2) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * s, k, w_row2);
+                }
+                tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * s, k, t0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            bool ok = true;
+            for (int i = 0; i < k_iters && ok; i++) {
+                const int s = i % stages;
+                ok = mbar_wait(full0 + 8 * s, (i / stages) & 1, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint64_t da = smem_desc(a), db = smem_desc(a + N_ACC * A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; kk++) {
+                    const uint32_t acc = (i | kk) != 0;
+                    mma_bf16(tmem, da + 2 * kk, db + 2 * kk, idesc, acc);
+                    if (N_ACC == 2) mma_bf16(tmem + BN, smem_desc(a + A_BYTES) + 2 * kk, db + 2 * kk, idesc, acc);
+                }
+                mma_commit(empty0 + 8 * s);
+            }
+            if (!ok) {
+                *reinterpret_cast<volatile int*>(&gave_up) = 1;
+                __threadfence_block();
+            }
+            mma_commit(acc_bar);   // also after a wait that ran out: the epilogue warps must not be left waiting
+        }
+    } else {
+        // Epilogue: this warp reads TMEM lanes 32 q .. 32 q + 31, i.e. outputs n0 + 32 q + lane, and half of the rows' columns.
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const int n = n0 + 32 * q + lane;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(acc_bar, 0, 3) && *reinterpret_cast<volatile int*>(&gave_up) == 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        tc_fence_after();
+        const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
+        if (ok) {
+            constexpr int MINE = BN / HALVES;
+            const int first = half * MINE;
+#pragma unroll 1
+            for (int cc = first; cc < first + MINE && cc < t_count; cc += 16) {
+                uint32_t v[16], u[16];
+                tmem_load16(taddr + cc, v);
+                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + cc, u);
+                tmem_load_wait();
+                if (n >= p.N) continue;
+                float r[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (cc + j >= t_count) break;
+                    const size_t at = (size_t)(t0 + cc + j) * p.N + n;
+                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    else ((float*)p.out)[at] = r[j];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int BN, int EPI>
+static int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, TcGroupParams p, int max_tiles, cudaStream_t s) {
+    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = N_ACC * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    int stages = (TC_SMEM_LIMIT - 1024) / STAGE_BYTES;
+    if (stages > 12) stages = 12;
+    // Few rows a matrix: the product streams weights, and two blocks on an SM keep more loads in flight than one.
+    const int half_stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
+    if (BN <= 64 && half_stages >= 4 && stages > half_stages) stages = half_stages;
+    if (stages > k_iters) stages = k_iters < 2 ? 2 : k_iters;
+    p.stages = stages;
+    const int smem = stages * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+        if (e != cudaSuccess) {
+            bc_set_error("gemm_tc_grouped: cannot raise the shared memory limit: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid((p.N + TC_BM - 1) / TC_BM, max_tiles);
+    cudaError_t e = bc_launch(gemm_tc_grouped_kernel<BN, EPI>, grid, dim3(tc_threads(BN)), (size_t)smem, s, mw, mx, p);
+    if (e != cudaSuccess) {
+        bc_set_error("gemm_tc_grouped: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    BC_LAUNCH_STATUS();
+}
+
+// X [rows, K] bf16, sorted by matrix; W [matrices, N, K] bf16 (gated: [matrices, 2 N, K], gate rows then up rows); out
+// [rows, N]: bf16 silu(gate) * up if gated, else float.  table: [0] tiles; then, a tile, matrix, first row, rows (at most
+// tile_rows, one of 16, 32, 64, 128); max_tiles: the most tiles the table can hold.  K a multiple of 8.
+extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, const int* table, int rows, int matrices, int N, int K, int gated,
+                                       int tile_rows, int max_tiles, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && matrices > 0 && N > 0 && K > 0, "gemm_tc_grouped: bad sizes rows=%d matrices=%d N=%d K=%d", rows, matrices, N, K);
+    BC_CHECK_ARG(K % 8 == 0, "gemm_tc_grouped: K=%d is not a multiple of 8 (TMA needs 16-byte row strides)", K);
+    BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_grouped: operands must be 16-byte aligned");
+    BC_CHECK_ARG(max_tiles > 0 && max_tiles <= 65535, "gemm_tc_grouped: %d tiles are too many", max_tiles);
+    BC_CHECK_ARG((long long)matrices * (gated ? 2 : 1) * N < 2147483647ll, "gemm_tc_grouped: too many weight rows");
+    if (rows == 0) return BC_OK;
+    CUtensorMap mw, mx;
+    const int matrix_rows = (gated ? 2 : 1) * N;
+    int st = weight_map(&mw, W, matrices * matrix_rows, K);
+    if (st != BC_OK) return st;
+    st = make_map(&mx, X, rows, K, tile_rows);
+    if (st != BC_OK) return st;
+    TcGroupParams p;
+    p.out = out;
+    p.table = table;
+    p.N = N;
+    p.K = K;
+    p.matrix_rows = matrix_rows;
+    p.stages = 0;
+#define GROUPED(BN)                                                                         \
+    case BN:                                                                                \
+        return gated ? launch_grouped<BN, EPI_SWIGLU>(mw, mx, p, max_tiles, s) : launch_grouped<BN, EPI_STORE_F32>(mw, mx, p, max_tiles, s);
+    switch (tile_rows) {
+        GROUPED(16) GROUPED(32) GROUPED(64) GROUPED(128)
+    }
+#undef GROUPED
+    bc_set_error("gemm_tc_grouped: no kernel for tiles of %d rows", tile_rows);
+    return BC_ERR_ARG;
+}
+
 // This unit's status word (0, or where a bounded wait gave up), its wait limit and its word
 // of host memory: bc_gemm_tc_status / _set_wait_cycles / _bind_host_word.
 TC_STATUS_EXPORTS(gemm_tc)

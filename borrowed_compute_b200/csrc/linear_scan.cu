@@ -20,102 +20,183 @@
 
 #define SCAN_NT 8          // threads that share a value channel, each with every eighth key channel
 #define SCAN_MAX_N 256
-#define SCAN_ROWS 8        // rows staged at a time
+#define SCAN_PT 32         // value channels a block: two a thread
 
-// A block takes (a slice of PT value channels, head, sequence): thread (tn, p) keeps S[n][p] for n = tn, tn + 8, ...
-// in registers over the sequence's rows.  The state lies in memory value channel by value channel,
-// [slot][head][P][N], so that the eight threads of a channel read neighbouring values.  The sums of a step
-// depend on the sizes alone: the same bits whether a row comes in a prompt or alone.
-template <int NJ, bool VECTOR_DECAY>
+__device__ __forceinline__ void scan_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT> __device__ __forceinline__ void scan_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory"); }
+
+// A block takes (a slice of 32 value channels, head, sequence): thread (tn, pl) keeps S[n][p] for n = tn, tn + 8, ... and
+// p = p0 + pl, p0 + 16 + pl in registers over the sequence's rows.  The state lies in memory value channel by value
+// channel, [slot][head][P][N], so that the eight threads of a channel read neighbouring values.  Rows are staged R at a time
+// in shared memory by asynchronous copies, the next R on their way while these are worked on (16 bytes a copy where every
+// run starts on such a border: VEC).  The sums of a step depend on the sizes alone: the same bits whether a row comes in a
+// prompt or alone.
+template <int NJ, bool VECTOR_DECAY, bool VEC>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const float* __restrict__ k, int k_stride, int k_rep,
                    const float* __restrict__ v, int v_stride, const float* __restrict__ decay, int d_stride,
                    const float* __restrict__ kscale, int c_stride, const float* __restrict__ skip, float out_scale,
                    float* __restrict__ state, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot, float* __restrict__ out,
-                   int H, int N, int P, int PT, int n_slots, int write_state) {
-    __shared__ float sq[SCAN_ROWS][SCAN_MAX_N], sk[SCAN_ROWS][SCAN_MAX_N], sd[SCAN_ROWS][VECTOR_DECAY ? SCAN_MAX_N : 1];
-    __shared__ float sv[SCAN_ROWS][16], sc[SCAN_ROWS];
+                   int H, int N, int P, int R, int n_slots, int write_state) {
+    extern __shared__ __align__(16) float staged[];
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(q); PDL_FRESH(k); PDL_FRESH(v); PDL_FRESH(decay); PDL_FRESH(kscale);
-    const int sidx = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * PT;
+    const int sidx = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * SCAN_PT;
     const int slot = seq_slot[sidx];
     const int row0 = seq_rows[sidx], n_rows = seq_rows[sidx + 1] - row0;
     if (slot < 0 || slot >= n_slots || n_rows <= 0) return;
-    const int tn = threadIdx.x % SCAN_NT, pl = threadIdx.x / SCAN_NT;
-    const int p = p0 + pl;
-    const bool live = pl < PT && p < P;
-    float* sp = state + (((size_t)slot * H + h) * P + (live ? p : 0)) * N;
-    float S[NJ];
+    const int tn = threadIdx.x % SCAN_NT, pl = threadIdx.x / SCAN_NT;         // 8 x 16 threads
+    const int pa = p0 + pl, pb = p0 + 16 + pl;
+    const bool live_a = pa < P, live_b = pb < P;
+    float* sa = state + (((size_t)slot * H + h) * P + (live_a ? pa : 0)) * N;
+    float* sb = state + (((size_t)slot * H + h) * P + (live_b ? pb : 0)) * N;
+    float Sa[NJ], Sb[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int n = tn + SCAN_NT * j;
-        S[j] = live && n < N ? sp[n] : 0.0f;
+        Sa[j] = live_a && n < N ? sa[n] : 0.0f;
+        Sb[j] = live_b && n < N ? sb[n] : 0.0f;
     }
     const float dskip = skip ? skip[h] : 0.0f;
-    const int threads = blockDim.x;
-    for (int t0 = 0; t0 < n_rows; t0 += SCAN_ROWS) {
-        const int nt = min(SCAN_ROWS, n_rows - t0);
+    // A stage: R rows of q, of k, of the decays (VECTOR_DECAY), of the block's 32 values, and the rows' two scalars.
+    const int n_arrays = VECTOR_DECAY ? 3 : 2;
+    const int stage_floats = R * (n_arrays * N + SCAN_PT + 2);
+    const float* qh = q + (size_t)(h / q_rep) * N;
+    const float* kh = k + (size_t)(h / k_rep) * N;
+    const float* dh = decay + (VECTOR_DECAY ? (size_t)h * N : (size_t)h);
+    const float* vh = v + (size_t)h * P + p0;
+    const int pv = min(SCAN_PT, P - p0);                    // values of this block a row
+    auto issue = [&](int chunk, int stage) {
+        const int t0 = chunk * R, nt = min(R, n_rows - t0);
+        float* sq = staged + (size_t)stage * stage_floats;
+        float* sk = sq + R * N;
+        float* sd = sk + R * N;
+        float* sv = sq + n_arrays * R * N;
+        float* sc = sv + R * SCAN_PT;
+        const size_t r0 = (size_t)(row0 + t0);
+        if (VEC) {
+            const int n4 = N / 4, pv4 = pv / 4;
+            for (int i = threadIdx.x; i < nt * n4; i += 128) {
+                const int t = i / n4, c = 4 * (i - t * n4);
+                scan_copy16(sq + t * N + c, qh + (r0 + t) * q_stride + c);
+                scan_copy16(sk + t * N + c, kh + (r0 + t) * k_stride + c);
+                if (VECTOR_DECAY) scan_copy16(sd + t * N + c, dh + (r0 + t) * d_stride + c);
+            }
+            for (int i = threadIdx.x; i < nt * pv4; i += 128) {
+                const int t = i / pv4, c = 4 * (i - t * pv4);
+                scan_copy16(sv + t * SCAN_PT + c, vh + (r0 + t) * v_stride + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * N; i += 128) {
+                const int t = i / N, c = i - t * N;
+                scan_copy4(sq + t * N + c, qh + (r0 + t) * q_stride + c);
+                scan_copy4(sk + t * N + c, kh + (r0 + t) * k_stride + c);
+                if (VECTOR_DECAY) scan_copy4(sd + t * N + c, dh + (r0 + t) * d_stride + c);
+            }
+            for (int i = threadIdx.x; i < nt * pv; i += 128) {
+                const int t = i / pv, c = i - t * pv;
+                scan_copy4(sv + t * SCAN_PT + c, vh + (r0 + t) * v_stride + c);
+            }
+        }
+        if ((int)threadIdx.x < nt) {
+            if (kscale) scan_copy4(sc + threadIdx.x, kscale + (r0 + threadIdx.x) * c_stride + h);
+            else sc[threadIdx.x] = 1.0f;
+            if (!VECTOR_DECAY) scan_copy4(sc + R + threadIdx.x, dh + (r0 + threadIdx.x) * d_stride);
+        }
+    };
+    const int chunks = (n_rows + R - 1) / R;
+    issue(0, 0);
+    scan_commit();
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        if (chunk + 1 < chunks) issue(chunk + 1, (chunk + 1) & 1);
+        scan_commit();
+        scan_wait<1>();
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * N; i += threads) {
-            const int t = i / N, n = i - t * N;
-            const size_t r = (size_t)(row0 + t0 + t);
-            sq[t][n] = q[r * q_stride + (size_t)(h / q_rep) * N + n];
-            sk[t][n] = k[r * k_stride + (size_t)(h / k_rep) * N + n];
-            if (VECTOR_DECAY) sd[t][n] = decay[r * d_stride + (size_t)h * N + n];
-        }
-        for (int i = threadIdx.x; i < nt * PT; i += threads) {
-            const int t = i / PT, c = i - t * PT;
-            sv[t][c] = p0 + c < P ? v[(size_t)(row0 + t0 + t) * v_stride + (size_t)h * P + p0 + c] : 0.0f;
-        }
-        if (threadIdx.x < nt) {
-            const size_t r = (size_t)(row0 + t0 + threadIdx.x);
-            sc[threadIdx.x] = kscale ? kscale[r * c_stride + h] : 1.0f;
-            if (!VECTOR_DECAY) sd[threadIdx.x][0] = decay[r * d_stride + h];
-        }
-        __syncthreads();
+        const int t0 = chunk * R, nt = min(R, n_rows - t0);
+        const float* sq = staged + (size_t)(chunk & 1) * stage_floats;
+        const float* sk = sq + R * N;
+        const float* sd = sk + R * N;
+        const float* sv = sq + n_arrays * R * N;
+        const float* sc = sv + R * SCAN_PT;
         for (int t = 0; t < nt; t++) {
-            const float vp = pl < PT ? sv[t][pl] : 0.0f;
-            const float cv = sc[t] * vp;
-            const float a0 = VECTOR_DECAY ? 0.0f : sd[t][0];
-            float o = 0.0f;
+            const float va = pl < pv ? sv[t * SCAN_PT + pl] : 0.0f, vb = 16 + pl < pv ? sv[t * SCAN_PT + 16 + pl] : 0.0f;
+            const float ca = sc[t] * va, cb = sc[t] * vb;
+            const float a0 = VECTOR_DECAY ? 0.0f : sc[R + t];
+            float oa = 0.0f, ob = 0.0f;
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const int n = tn + SCAN_NT * j;
                 if (n < N) {
-                    S[j] = fmaf(VECTOR_DECAY ? sd[t][n] : a0, S[j], sk[t][n] * cv);
-                    o = fmaf(S[j], sq[t][n], o);
+                    const float a = VECTOR_DECAY ? sd[t * N + n] : a0, kk = sk[t * N + n], qq = sq[t * N + n];
+                    Sa[j] = fmaf(a, Sa[j], kk * ca);
+                    Sb[j] = fmaf(a, Sb[j], kk * cb);
+                    oa = fmaf(Sa[j], qq, oa);
+                    ob = fmaf(Sb[j], qq, ob);
                 }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (live && tn == 0) out[(size_t)(row0 + t0 + t) * H * P + (size_t)h * P + p] = fmaf(dskip, vp, out_scale * o);
+            oa += __shfl_xor_sync(0xffffffffu, oa, 1);
+            ob += __shfl_xor_sync(0xffffffffu, ob, 1);
+            oa += __shfl_xor_sync(0xffffffffu, oa, 2);
+            ob += __shfl_xor_sync(0xffffffffu, ob, 2);
+            oa += __shfl_xor_sync(0xffffffffu, oa, 4);
+            ob += __shfl_xor_sync(0xffffffffu, ob, 4);
+            float* o = out + (size_t)(row0 + t0 + t) * H * P + (size_t)h * P;
+            if (live_a && tn == 0) o[pa] = fmaf(dskip, va, out_scale * oa);
+            if (live_b && tn == 1) o[pb] = fmaf(dskip, vb, out_scale * ob);
         }
+        __syncthreads();          // all have read the stage before the copies of the chunk after next land in it
     }
-    if (write_state && live) {
+    if (write_state) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
             const int n = tn + SCAN_NT * j;
-            if (n < N) sp[n] = S[j];
+            if (live_a && n < N) sa[n] = Sa[j];
+            if (live_b && n < N) sb[n] = Sb[j];
         }
     }
 }
 
-template <bool VD>
-static int scan_launch(int NJ, dim3 grid, dim3 block, cudaStream_t s, const float* q, int q_stride, int q_rep, const float* k, int k_stride,
+template <int NJ, bool VD, bool VEC>
+static cudaError_t scan_launch_one(dim3 grid, size_t smem, cudaStream_t s, const float* q, int q_stride, int q_rep, const float* k, int k_stride,
+                                   int k_rep, const float* v, int v_stride, const float* decay, int d_stride, const float* kscale, int c_stride,
+                                   const float* skip, float out_scale, float* state, const int* seq_rows, const int* seq_slot, float* out, int H,
+                                   int N, int P, int R, int n_slots, int write_state) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<NJ, VD, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return bc_launch(linear_scan_kernel<NJ, VD, VEC>, grid, dim3(128), smem, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride,
+                     kscale, c_stride, skip, out_scale, state, seq_rows, seq_slot, out, H, N, P, R, n_slots, write_state);
+}
+
+template <bool VD, bool VEC>
+static int scan_launch(int NJ, dim3 grid, size_t smem, cudaStream_t s, const float* q, int q_stride, int q_rep, const float* k, int k_stride,
                        int k_rep, const float* v, int v_stride, const float* decay, int d_stride, const float* kscale, int c_stride,
                        const float* skip, float out_scale, float* state, const int* seq_rows, const int* seq_slot, float* out, int H, int N,
-                       int P, int PT, int n_slots, int write_state) {
-#define SCAN_CASE(J)                                                                                                                        \
-    case J:                                                                                                                                 \
-        bc_launch(linear_scan_kernel<J, VD>, grid, block, 0, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, \
-                  c_stride, skip, out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);                            \
+                       int P, int R, int n_slots, int write_state) {
+    cudaError_t e = cudaSuccess;
+#define SCAN_CASE(J)                                                                                                                         \
+    case J:                                                                                                                                  \
+        e = scan_launch_one<J, VD, VEC>(grid, smem, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, \
+                                        skip, out_scale, state, seq_rows, seq_slot, out, H, N, P, R, n_slots, write_state);                  \
         break;
     switch (NJ) {
-        SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(3) SCAN_CASE(4) SCAN_CASE(6) SCAN_CASE(8) SCAN_CASE(12) SCAN_CASE(16) SCAN_CASE(24) SCAN_CASE(32)
+        SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(12) SCAN_CASE(16) SCAN_CASE(24) SCAN_CASE(32)
     }
 #undef SCAN_CASE
+    if (e != cudaSuccess) {
+        bc_set_error("linear_scan: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     BC_LAUNCH_STATUS();
 }
 
@@ -132,16 +213,26 @@ extern "C" int bc_linear_scan(const float* q, int q_stride, int q_rep, const flo
     BC_CHECK_ARG(q_rep > 0 && k_rep > 0, "linear_scan: bad sharing of q (%d) or k (%d)", q_rep, k_rep);
     if (seqs == 0) return BC_OK;
     int nj = (N + SCAN_NT - 1) / SCAN_NT;
-    const int have[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32};
+    const int have[] = {1, 2, 4, 8, 12, 16, 24, 32};
     for (int c : have)
         if (c >= nj) { nj = c; break; }
-    const int PT = P >= 16 ? 16 : P;      // by the head's width alone
-    dim3 grid((P + PT - 1) / PT, H, seqs), block(PT * SCAN_NT < 32 ? 32 : (PT * SCAN_NT + 31) / 32 * 32);
-    if (vector_decay)
-        return scan_launch<true>(nj, grid, block, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, skip,
-                                 out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);
-    return scan_launch<false>(nj, grid, block, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, skip,
-                              out_scale, state, seq_rows, seq_slot, out, H, N, P, PT, n_slots, write_state);
+    // Rows a stage: sixteen, eight for the widest heads (two stages of q, k and decays must fit beside other blocks).
+    const int R = N > 128 ? 8 : 16;
+    const size_t smem = 2 * (size_t)R * ((vector_decay ? 3 : 2) * N + SCAN_PT + 2) * sizeof(float);
+    // 16 bytes a copy where every run of every row starts on a 16-byte border and is a multiple of 16 bytes long.
+    const bool vec = N % 4 == 0 && P % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && (!vector_decay || d_stride % 4 == 0) &&
+                     (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0 && (!vector_decay || (uintptr_t)decay % 16 == 0);
+    dim3 grid((P + SCAN_PT - 1) / SCAN_PT, H, seqs);
+#define SCAN_GO(VD, VEC)                                                                                                                    \
+    return scan_launch<VD, VEC>(nj, grid, smem, s, q, q_stride, q_rep, k, k_stride, k_rep, v, v_stride, decay, d_stride, kscale, c_stride, skip, \
+                                out_scale, state, seq_rows, seq_slot, out, H, N, P, R, n_slots, write_state)
+    if (vector_decay) {
+        if (vec) SCAN_GO(true, true);
+        SCAN_GO(true, false);
+    }
+    if (vec) SCAN_GO(false, true);
+    SCAN_GO(false, false);
+#undef SCAN_GO
 }
 
 // ------------------------------------------------------------------------------- ssd_prepare

@@ -21,8 +21,15 @@
 #define MOE_MAX_TOP 16
 
 // -------------------------------------------------------------------------------------- route
+// Four neighbouring values of a row as floats (the row starts on a 16-byte border and k is a multiple of 4).
+__device__ __forceinline__ float4 route_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 route_load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+
 template <class T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const int* __restrict__ row_slot, int* __restrict__ choice,
                  float* __restrict__ weight, int E, int K, int top, int softmax, int renorm) {
     extern __shared__ float score[];
@@ -39,10 +46,19 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
         return;
     }
     const T* x = h + (size_t)r * K;
+    // One warp an expert; a lane's share of the sum, and the order of the shares, depend on K alone.
+    const bool wide = K % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)router % 16 == 0;
     for (int e = warp; e < E; e += warps) {
         const float* w = router + (size_t)e * K;
         float z = 0.0f;
-        for (int k = lane; k < K; k += 32) z = fmaf(to_f32(x[k]), w[k], z);
+        if (wide) {
+            for (int k = 4 * lane; k < K; k += 128) {
+                const float4 a = route_load4(x + k), b = route_load4(w + k);
+                z = fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, z))));
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) z = fmaf(to_f32(x[k]), w[k], z);
+        }
         z = warp_sum(z);
         if (lane == 0) score[e] = z == z ? z : -INFINITY;      // a row of not-a-numbers still chooses experts that exist
     }
@@ -103,7 +119,7 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ 
 // One block: where every expert's rows start in sorted order, and the tiles.  table: [0] the number of tiles, then for tile t
 // at 1 + 3 t: expert, first sorted place, rows.
 __global__ void __launch_bounds__(32) moe_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ table,
-                                                        int max_tiles) {
+                                                        int max_tiles, int tile_rows) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(counts);
@@ -112,10 +128,10 @@ __global__ void __launch_bounds__(32) moe_offsets_kernel(const int* __restrict__
     for (int e = 0; e < E; e++) {
         offsets[e] = at;
         const int n = counts[e];
-        for (int s = 0; s < n && tiles < max_tiles; s += MOE_BM) {
+        for (int s = 0; s < n && tiles < max_tiles; s += tile_rows) {
             table[1 + 3 * tiles] = e;
             table[2 + 3 * tiles] = at + s;
-            table[3 + 3 * tiles] = min(MOE_BM, n - s);
+            table[3 + 3 * tiles] = min(tile_rows, n - s);
             tiles++;
         }
         at += n;
@@ -253,6 +269,28 @@ moe_product_kernel(const T* __restrict__ X, const T* __restrict__ W, const int* 
     }
 }
 
+// ------------------------------------------------------------------------------------- gather
+// sorted[j] = weight[perm[j]] * x[perm[j] / top] (the weight on the expert's input) or x[perm[j] / top], for the sorted places
+// j below offsets[E], the pairs that chose an expert; the places past them hold nothing that is ever written out.
+template <class T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets, const float* __restrict__ weight,
+                  T* __restrict__ sorted, int E, int K, int top, int weight_on_input) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(x); PDL_FRESH(perm); PDL_FRESH(offsets); PDL_FRESH(weight);
+    const int j = blockIdx.x;
+    T* dst = sorted + (size_t)j * K;
+    if (j >= offsets[E]) {
+        for (int c = threadIdx.x; c < K; c += blockDim.x) dst[c] = from_f32<T>(0.0f);
+        return;
+    }
+    const int pair = perm[j];
+    const float w = weight_on_input ? weight[pair] : 1.0f;
+    const T* src = x + (size_t)(pair / top) * K;
+    for (int c = threadIdx.x; c < K; c += blockDim.x) dst[c] = from_f32<T>(w * to_f32(src[c]));
+}
+
 // ------------------------------------------------------------------------------------ combine
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ choice, const int* __restrict__ place, const float* __restrict__ weight,
@@ -280,7 +318,7 @@ static int route(const void* h, const float* router, const int* row_slot, int* c
                  int renorm, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 8192, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
     if (rows == 0) return BC_OK;
-    bc_launch(moe_route_kernel<T>, dim3(rows), dim3(128), (size_t)E * sizeof(float), s, (const T*)h, router, row_slot, choice, weight, E, K, top,
+    bc_launch(moe_route_kernel<T>, dim3(rows), dim3(256), (size_t)E * sizeof(float), s, (const T*)h, router, row_slot, choice, weight, E, K, top,
               softmax, renorm);
     BC_LAUNCH_STATUS();
 }
@@ -295,14 +333,17 @@ extern "C" int bc_moe_route_bf16(const void* h, const float* router, const int* 
     return route<bf16>(h, router, row_slot, choice, weight, rows, E, K, top, softmax, renorm, s);
 }
 
-extern "C" int bc_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
+// The most tiles of `tile_rows` sorted rows that `pairs` rows over E experts can make (every expert may end with a part of a tile).
+extern "C" int bc_moe_max_tiles(int pairs, int E, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + E; }
+extern "C" int bc_moe_simt_tile_rows() { return MOE_BM; }
 
-// choice: [pairs]; counts: [E]; offsets: [E + 1]; table: [1 + 3 * bc_moe_max_tiles(pairs, E)]; perm, place: [pairs].
-extern "C" int bc_moe_plan(const int* choice, int pairs, int E, int* counts, int* offsets, int* table, int* perm, int* place, cudaStream_t s) {
-    BC_CHECK_ARG(pairs >= 0 && E > 0 && E <= 65535, "moe_plan: bad sizes pairs=%d E=%d", pairs, E);
+// choice: [pairs]; counts: [E]; offsets: [E + 1]; table: [1 + 3 * bc_moe_max_tiles(pairs, E, tile_rows)]; perm, place: [pairs].
+extern "C" int bc_moe_plan(const int* choice, int pairs, int E, int tile_rows, int* counts, int* offsets, int* table, int* perm, int* place,
+                           cudaStream_t s) {
+    BC_CHECK_ARG(pairs >= 0 && E > 0 && E <= 65535 && tile_rows > 0, "moe_plan: bad sizes pairs=%d E=%d tile_rows=%d", pairs, E, tile_rows);
     if (pairs == 0) return BC_OK;
     bc_launch(moe_count_kernel, dim3(E), dim3(256), 0, s, choice, pairs, counts);
-    bc_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, E, offsets, table, bc_moe_max_tiles(pairs, E));
+    bc_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, E, offsets, table, bc_moe_max_tiles(pairs, E, tile_rows), tile_rows);
     bc_launch(moe_fill_kernel, dim3(E), dim3(256), 0, s, choice, pairs, (const int*)offsets, perm, place);
     BC_LAUNCH_STATUS();
 }
@@ -312,7 +353,7 @@ static int products(int gated, const void* X, const void* W, const int* table, c
                     int N, int K, int top, int weight_on_input, cudaStream_t s) {
     BC_CHECK_ARG(pairs >= 0 && E > 0 && N > 0 && K > 0 && top > 0, "moe_product: bad sizes pairs=%d E=%d N=%d K=%d", pairs, E, N, K);
     if (pairs == 0) return BC_OK;
-    const int tiles = bc_moe_max_tiles(pairs, E);
+    const int tiles = bc_moe_max_tiles(pairs, E, MOE_BM);
     BC_CHECK_ARG(tiles <= 65535, "moe_product: %d tiles are too many", tiles);
     dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
     if (gated)
@@ -331,6 +372,24 @@ extern "C" int bc_moe_product_f32(int gated, const void* X, const void* W, const
 extern "C" int bc_moe_product_bf16(int gated, const void* X, const void* W, const int* table, const int* perm, const float* weight, void* out,
                                    int pairs, int E, int N, int K, int top, int weight_on_input, cudaStream_t s) {
     return products<bf16>(gated, X, W, table, perm, weight, out, pairs, E, N, K, top, weight_on_input, s);
+}
+
+template <class T>
+static int gather(const void* x, const int* perm, const int* offsets, const float* weight, void* sorted, int pairs, int E, int K, int top,
+                  int weight_on_input, cudaStream_t s) {
+    BC_CHECK_ARG(pairs >= 0 && E > 0 && K > 0 && top > 0, "moe_gather: bad sizes pairs=%d E=%d K=%d top=%d", pairs, E, K, top);
+    if (pairs == 0) return BC_OK;
+    bc_launch(moe_gather_kernel<T>, dim3(pairs), dim3(K >= 2048 ? 256 : 128), 0, s, (const T*)x, perm, offsets, weight, (T*)sorted, E, K, top, weight_on_input);
+    BC_LAUNCH_STATUS();
+}
+// x: [rows, K]; sorted: [pairs, K]; perm: [pairs]; offsets: [E + 1]; weight: [pairs] in the order of (row, choice).
+extern "C" int bc_moe_gather_f32(const void* x, const int* perm, const int* offsets, const float* weight, void* sorted, int pairs, int E, int K,
+                                 int top, int weight_on_input, cudaStream_t s) {
+    return gather<float>(x, perm, offsets, weight, sorted, pairs, E, K, top, weight_on_input, s);
+}
+extern "C" int bc_moe_gather_bf16(const void* x, const int* perm, const int* offsets, const float* weight, void* sorted, int pairs, int E, int K,
+                                  int top, int weight_on_input, cudaStream_t s) {
+    return gather<bf16>(x, perm, offsets, weight, sorted, pairs, E, K, top, weight_on_input, s);
 }
 
 // y: [pairs, width] float in sorted order; residual: [rows, width] float.

@@ -145,7 +145,7 @@ _CLASS_OF = {
     "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
     "bc_short_conv": "short convolution", "bc_norm_pair": "norm", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
     "bc_linear_scan": "recurrence", "bc_ssd_prepare": "recurrence set-up", "bc_gla_decay": "recurrence set-up", "bc_gated_norm": "gated norm",
-    "bc_moe_product": "expert product", "bc_moe": "routing", "bc_softcap": "softcap", "bc_reentry": "re-entry",
+    "bc_moe_product": "expert product", "bc_gemm_tc_grouped": "expert product", "bc_moe": "routing", "bc_softcap": "softcap", "bc_reentry": "re-entry",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
 }
 
@@ -898,21 +898,70 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Te
           _c_int(K), _c_int(top), _c_int(1 if softmax else 0), _c_int(1 if renorm else 0), _stream())
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
-    return int(_fn("bc_moe_max_tiles")(_c_int(pairs), _c_int(experts)))
+def moe_simt_tile_rows() -> int:
+    """Sorted rows a tile of the CUDA-core expert product takes."""
+    return int(_fn("bc_moe_simt_tile_rows")())
+
+
+def moe_max_tiles(pairs: int, experts: int, tile_rows: Optional[int] = None) -> int:
+    return int(_fn("bc_moe_max_tiles")(_c_int(pairs), _c_int(experts), _c_int(moe_simt_tile_rows() if tile_rows is None else tile_rows)))
 
 
 def moe_plan(choice: torch.Tensor, experts: int, counts: torch.Tensor, offsets: torch.Tensor, table: torch.Tensor, perm: torch.Tensor,
-             place: torch.Tensor) -> None:
+             place: torch.Tensor, tile_rows: Optional[int] = None) -> None:
     """Sorts the (row, choice) pairs by expert: perm[j] names the pair at sorted place j, place[pair] its place; ``table`` lists tiles
-    of sorted rows that lie in one expert ([0]: how many; then expert, first place, rows for each)."""
+    of at most ``tile_rows`` sorted rows (default: what the CUDA-core product takes) that lie in one expert ([0]: how many; then
+    expert, first place, rows for each)."""
+    tile_rows = moe_simt_tile_rows() if tile_rows is None else int(tile_rows)
     for t, name in ((choice, "choice"), (counts, "counts"), (offsets, "offsets"), (table, "table"), (perm, "perm"), (place, "place")):
         _need(t, name, torch.int32)
     pairs = choice.numel()
-    if counts.numel() < experts or offsets.numel() < experts + 1 or table.numel() < 1 + 3 * moe_max_tiles(pairs, experts) or perm.numel() < pairs \
+    if counts.numel() < experts or offsets.numel() < experts + 1 or table.numel() < 1 + 3 * moe_max_tiles(pairs, experts, tile_rows) or perm.numel() < pairs \
             or place.numel() < pairs:
         raise KernelError("moe_plan: a buffer is too small")
-    _call(_fn("bc_moe_plan"), _ptr(choice), _c_int(pairs), _c_int(experts), _ptr(counts), _ptr(offsets), _ptr(table), _ptr(perm), _ptr(place), _stream())
+    _call(_fn("bc_moe_plan"), _ptr(choice), _c_int(pairs), _c_int(experts), _c_int(tile_rows), _ptr(counts), _ptr(offsets), _ptr(table), _ptr(perm),
+          _ptr(place), _stream())
+
+
+def moe_gather(x: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, experts: int, top: int,
+               weight_on_input: bool) -> None:
+    """out[j] = x[row of the pair at sorted place j], times the pair's weight with ``weight_on_input``; places past the pairs that
+    chose an expert are cleared."""
+    _need(x, "x")
+    _need(out, "out", x.dtype)
+    _need(perm, "perm", torch.int32)
+    _need(offsets, "offsets", torch.int32)
+    _need(weight, "weight", torch.float32)
+    pairs, K = out.shape
+    if x.shape[1] != K or perm.numel() < pairs or offsets.numel() < experts + 1 or weight.numel() < pairs:
+        raise KernelError(f"moe_gather: x {tuple(x.shape)}, out {tuple(out.shape)} do not fit")
+    _call(_fn("bc_moe_gather_" + _suffix(x.dtype)), _ptr(x), _ptr(perm), _ptr(offsets), _ptr(weight), _ptr(out), _c_int(pairs), _c_int(experts),
+          _c_int(K), _c_int(top), _c_int(1 if weight_on_input else 0), _stream())
+
+
+GROUPED_TILE_ROWS = (16, 32, 64, 128)
+
+
+def gemm_tc_grouped_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core product over groups of rows takes these operands (bf16, K a multiple of 8, 16-byte aligned)."""
+    return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.Tensor, gated: bool, tile_rows: int, max_tiles: int) -> None:
+    """Rows of x [rows, K] sorted by the matrix they meet, times that matrix of w [matrices, N, K] (``gated``: [matrices, 2 N, K],
+    gate rows then up rows, and out = silu(gate) * up in bf16; else out float32 [rows, N]), on the tcgen05 tensor cores.  ``table``
+    ([0]: tiles; then matrix, first row, rows a tile of at most ``tile_rows``) comes from ``moe_plan`` with the same ``tile_rows``."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.bfloat16 if gated else torch.float32)
+    _need(table, "table", torch.int32)
+    rows, K = x.shape
+    matrices, n_w, kw = w.shape
+    N = n_w // 2 if gated else n_w
+    if kw != K or tuple(out.shape) != (rows, N) or tile_rows not in GROUPED_TILE_ROWS or table.numel() < 1 + 3 * max_tiles:
+        raise KernelError(f"gemm_tc_grouped: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, tiles of {tile_rows} do not fit")
+    _call(_fn("bc_gemm_tc_grouped_bf16"), _ptr(x), _ptr(w), _ptr(out), _ptr(table), _c_int(rows), _c_int(matrices), _c_int(N), _c_int(K),
+          _c_int(1 if gated else 0), _c_int(tile_rows), _c_int(max_tiles), _stream())
 
 
 def moe_product(gated: bool, x: torch.Tensor, w: torch.Tensor, table: torch.Tensor, perm: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,

@@ -22,6 +22,9 @@ from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, TensorSpec
 from .mlp import SwiGLU
 
 
+force_simt = False      # tests: the CUDA-core products (the checked twin) for bfloat16 too
+
+
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, experts: int, top: int, intermediate_size: int, shared_size: int = 0, score: str = "sigmoid",
@@ -62,13 +65,26 @@ class RoutedExperts(FeedForward):
         choice = torch.empty((rows, top), **i32)
         weight = torch.empty((rows, top), dtype=torch.float32, device=dev)
         ops.moe_route(x, self.router, ctx.row_slot, choice, weight, softmax=self.softmax, renorm=self.renormalize)
-        ints = torch.empty(E + (E + 1) + (1 + 3 * ops.moe_max_tiles(pairs, E)) + 2 * pairs, **i32)
-        counts, offsets, table, perm, place = torch.split(ints, [E, E + 1, 1 + 3 * ops.moe_max_tiles(pairs, E), pairs, pairs])
-        ops.moe_plan(choice, E, counts, offsets, table, perm, place)
+        # bfloat16 whose widths the tensor cores take: the rows are gathered in sorted order (times their weights: the weight
+        # multiplies the expert's input) and both products run on tcgen05 tiles; else on the CUDA cores, gathering as they go.
+        tensor_cores = not force_simt and self.intermediate_size % 8 == 0 and ops.gemm_tc_grouped_accepts(x, self.w_gate_up)
+        tile_rows = ops.moe_simt_tile_rows()
+        if tensor_cores:
+            tile_rows = next((t for t in ops.GROUPED_TILE_ROWS if pairs <= t * E), ops.GROUPED_TILE_ROWS[-1])      # by the rows an expert gets on average
+        max_tiles = ops.moe_max_tiles(pairs, E, tile_rows)
+        ints = torch.empty(E + (E + 1) + (1 + 3 * max_tiles) + 2 * pairs, **i32)
+        counts, offsets, table, perm, place = torch.split(ints, [E, E + 1, 1 + 3 * max_tiles, pairs, pairs])
+        ops.moe_plan(choice, E, counts, offsets, table, perm, place, tile_rows)
         act = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=dev)
-        ops.moe_product(True, x, self.w_gate_up, table, perm, weight, act, top, weight_on_input=self.on_input)
         y = torch.empty((pairs, self.hidden_size), dtype=torch.float32, device=dev)
-        ops.moe_product(False, act, self.w_down, table, perm, weight, y, top)
+        if tensor_cores:
+            xs = torch.empty((pairs, self.hidden_size), dtype=x.dtype, device=dev)
+            ops.moe_gather(x, perm, offsets, weight, xs, E, top, weight_on_input=self.on_input)
+            ops.gemm_tc_grouped(xs, self.w_gate_up, act, table, True, tile_rows, max_tiles)
+            ops.gemm_tc_grouped(act, self.w_down, y, table, False, tile_rows, max_tiles)
+        else:
+            ops.moe_product(True, x, self.w_gate_up, table, perm, weight, act, top, weight_on_input=self.on_input)
+            ops.moe_product(False, act, self.w_down, table, perm, weight, y, top)
         ops.moe_combine(y, choice, place, weight, residual, weight_on_output=not self.on_input)
         if self.shared is not None:
             self.shared.forward(x, residual, ctx)
