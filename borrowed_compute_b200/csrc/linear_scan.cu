@@ -35,8 +35,10 @@ template <int LEFT> __device__ __forceinline__ void scan_wait() { asm volatile("
 // p = p0 + pl, p0 + 16 + pl in registers over the sequence's rows.  The state lies in memory value channel by value
 // channel, [slot][head][P][N], so that the eight threads of a channel read neighbouring values.  Rows are staged R at a time
 // in shared memory by asynchronous copies, the next R on their way while these are worked on (16 bytes a copy where every
-// run starts on such a border: VEC).  The sums of a step depend on the sizes alone: the same bits whether a row comes in a
-// prompt or alone.
+// run starts on such a border: VEC).  A staged row of q, k or decays is NP = 8 NJ values long, zeros past the N that exist,
+// so that the loop over a thread's key channels has no test in it: with one, every channel's loads waited behind the
+// branch of the channel before (75 clocks a channel measured, 1,500 a step of 128 channels).  The sums of a step depend on
+// the sizes alone: the same bits whether a row comes in a prompt or alone.
 template <int NJ, bool VECTOR_DECAY, bool VEC>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const float* __restrict__ k, int k_stride, int k_rep,
@@ -66,8 +68,18 @@ linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const f
     }
     const float dskip = skip ? skip[h] : 0.0f;
     // A stage: R rows of q, of k, of the decays (VECTOR_DECAY), of the block's 32 values, and the rows' two scalars.
+    constexpr int NP = SCAN_NT * NJ;
     const int n_arrays = VECTOR_DECAY ? 3 : 2;
-    const int stage_floats = R * (n_arrays * N + SCAN_PT + 2);
+    const int stage_floats = R * (n_arrays * NP + SCAN_PT + 2);
+    if (NP != N) {
+        // The padding of every staged row, once: no copy ever lands there.
+        const int pad = NP - N;
+        for (int i = threadIdx.x; i < 2 * n_arrays * R * pad; i += 128) {
+            const int row = i / pad, c = N + i - row * pad;           // row counts over stages, arrays and rows
+            const int stage = row / (n_arrays * R), in_stage = row - stage * (n_arrays * R);
+            staged[(size_t)stage * stage_floats + (size_t)in_stage * NP + c] = 0.0f;
+        }
+    }
     const float* qh = q + (size_t)(h / q_rep) * N;
     const float* kh = k + (size_t)(h / k_rep) * N;
     const float* dh = decay + (VECTOR_DECAY ? (size_t)h * N : (size_t)h);
@@ -76,18 +88,18 @@ linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const f
     auto issue = [&](int chunk, int stage) {
         const int t0 = chunk * R, nt = min(R, n_rows - t0);
         float* sq = staged + (size_t)stage * stage_floats;
-        float* sk = sq + R * N;
-        float* sd = sk + R * N;
-        float* sv = sq + n_arrays * R * N;
+        float* sk = sq + R * NP;
+        float* sd = sk + R * NP;
+        float* sv = sq + n_arrays * R * NP;
         float* sc = sv + R * SCAN_PT;
         const size_t r0 = (size_t)(row0 + t0);
         if (VEC) {
             const int n4 = N / 4, pv4 = pv / 4;
             for (int i = threadIdx.x; i < nt * n4; i += 128) {
                 const int t = i / n4, c = 4 * (i - t * n4);
-                scan_copy16(sq + t * N + c, qh + (r0 + t) * q_stride + c);
-                scan_copy16(sk + t * N + c, kh + (r0 + t) * k_stride + c);
-                if (VECTOR_DECAY) scan_copy16(sd + t * N + c, dh + (r0 + t) * d_stride + c);
+                scan_copy16(sq + t * NP + c, qh + (r0 + t) * q_stride + c);
+                scan_copy16(sk + t * NP + c, kh + (r0 + t) * k_stride + c);
+                if (VECTOR_DECAY) scan_copy16(sd + t * NP + c, dh + (r0 + t) * d_stride + c);
             }
             for (int i = threadIdx.x; i < nt * pv4; i += 128) {
                 const int t = i / pv4, c = 4 * (i - t * pv4);
@@ -96,9 +108,9 @@ linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const f
         } else {
             for (int i = threadIdx.x; i < nt * N; i += 128) {
                 const int t = i / N, c = i - t * N;
-                scan_copy4(sq + t * N + c, qh + (r0 + t) * q_stride + c);
-                scan_copy4(sk + t * N + c, kh + (r0 + t) * k_stride + c);
-                if (VECTOR_DECAY) scan_copy4(sd + t * N + c, dh + (r0 + t) * d_stride + c);
+                scan_copy4(sq + t * NP + c, qh + (r0 + t) * q_stride + c);
+                scan_copy4(sk + t * NP + c, kh + (r0 + t) * k_stride + c);
+                if (VECTOR_DECAY) scan_copy4(sd + t * NP + c, dh + (r0 + t) * d_stride + c);
             }
             for (int i = threadIdx.x; i < nt * pv; i += 128) {
                 const int t = i / pv, c = i - t * pv;
@@ -120,27 +132,33 @@ linear_scan_kernel(const float* __restrict__ q, int q_stride, int q_rep, const f
         scan_wait<1>();
         __syncthreads();
         const int t0 = chunk * R, nt = min(R, n_rows - t0);
-        const float* sq = staged + (size_t)(chunk & 1) * stage_floats;
-        const float* sk = sq + R * N;
-        const float* sd = sk + R * N;
-        const float* sv = sq + n_arrays * R * N;
+        const float* sq = staged + (size_t)(chunk & 1) * stage_floats + tn;
+        const float* sk = sq + R * NP;
+        const float* sd = sk + R * NP;
+        const float* sv = staged + (size_t)(chunk & 1) * stage_floats + n_arrays * R * NP;
         const float* sc = sv + R * SCAN_PT;
+        // Two steps are unrolled together, so that one's shuffles and store pass while the other's loads and sums run.
+#pragma unroll 2
         for (int t = 0; t < nt; t++) {
             const float va = pl < pv ? sv[t * SCAN_PT + pl] : 0.0f, vb = 16 + pl < pv ? sv[t * SCAN_PT + 16 + pl] : 0.0f;
             const float ca = sc[t] * va, cb = sc[t] * vb;
             const float a0 = VECTOR_DECAY ? 0.0f : sc[R + t];
-            float oa = 0.0f, ob = 0.0f;
+            float oa = 0.0f, ob = 0.0f, oa2 = 0.0f, ob2 = 0.0f;      // even and odd channels apart: two chains half as long
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
-                const int n = tn + SCAN_NT * j;
-                if (n < N) {
-                    const float a = VECTOR_DECAY ? sd[t * N + n] : a0, kk = sk[t * N + n], qq = sq[t * N + n];
-                    Sa[j] = fmaf(a, Sa[j], kk * ca);
-                    Sb[j] = fmaf(a, Sb[j], kk * cb);
+                const float a = VECTOR_DECAY ? sd[t * NP + SCAN_NT * j] : a0, kk = sk[t * NP + SCAN_NT * j], qq = sq[t * NP + SCAN_NT * j];
+                Sa[j] = fmaf(a, Sa[j], kk * ca);
+                Sb[j] = fmaf(a, Sb[j], kk * cb);
+                if (j & 1) {
+                    oa2 = fmaf(Sa[j], qq, oa2);
+                    ob2 = fmaf(Sb[j], qq, ob2);
+                } else {
                     oa = fmaf(Sa[j], qq, oa);
                     ob = fmaf(Sb[j], qq, ob);
                 }
             }
+            oa += oa2;
+            ob += ob2;
             oa += __shfl_xor_sync(0xffffffffu, oa, 1);
             ob += __shfl_xor_sync(0xffffffffu, ob, 1);
             oa += __shfl_xor_sync(0xffffffffu, oa, 2);
@@ -218,7 +236,7 @@ extern "C" int bc_linear_scan(const float* q, int q_stride, int q_rep, const flo
         if (c >= nj) { nj = c; break; }
     // Rows a stage: sixteen, eight for the widest heads (two stages of q, k and decays must fit beside other blocks).
     const int R = N > 128 ? 8 : 16;
-    const size_t smem = 2 * (size_t)R * ((vector_decay ? 3 : 2) * N + SCAN_PT + 2) * sizeof(float);
+    const size_t smem = 2 * (size_t)R * ((vector_decay ? 3 : 2) * SCAN_NT * nj + SCAN_PT + 2) * sizeof(float);
     // 16 bytes a copy where every run of every row starts on a 16-byte border and is a multiple of 16 bytes long.
     const bool vec = N % 4 == 0 && P % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && (!vector_decay || d_stride % 4 == 0) &&
                      (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0 && (!vector_decay || (uintptr_t)decay % 16 == 0);

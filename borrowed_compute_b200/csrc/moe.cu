@@ -28,42 +28,59 @@ __device__ __forceinline__ float4 route_load4(const bf16* p) {
     return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
 }
 
+#define ROUTE_ROWS 4        // rows a block: every expert's weights are read once for four rows
+
 template <class T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const int* __restrict__ row_slot, int* __restrict__ choice,
-                 float* __restrict__ weight, int E, int K, int top, int softmax, int renorm) {
-    extern __shared__ float score[];
+                 float* __restrict__ weight, int rows, int E, int K, int top, int softmax, int renorm) {
+    extern __shared__ float score_all[];                    // [ROUTE_ROWS][E]
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(h);
-    const int r = blockIdx.x;
+    const int r0 = blockIdx.x * ROUTE_ROWS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    // One warp an expert, four rows at a time; a lane's share of a row's sum, and the order of the shares, depend on K alone.
+    const bool wide = K % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)router % 16 == 0;
+    const T* x[ROUTE_ROWS];
+#pragma unroll
+    for (int i = 0; i < ROUTE_ROWS; i++) x[i] = h + (size_t)min(r0 + i, rows - 1) * K;
+    for (int e = warp; e < E; e += warps) {
+        const float* w = router + (size_t)e * K;
+        float z[ROUTE_ROWS] = {};
+        if (wide) {
+            for (int k = 4 * lane; k < K; k += 128) {
+                const float4 b = route_load4(w + k);
+#pragma unroll
+                for (int i = 0; i < ROUTE_ROWS; i++) {
+                    const float4 a = route_load4(x[i] + k);
+                    z[i] = fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, z[i]))));
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                const float b = w[k];
+#pragma unroll
+                for (int i = 0; i < ROUTE_ROWS; i++) z[i] = fmaf(to_f32(x[i][k]), b, z[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < ROUTE_ROWS; i++) {
+            const float v = warp_sum(z[i]);
+            if (lane == 0) score_all[i * E + e] = v == v ? v : -INFINITY;      // a row of not-a-numbers still chooses experts that exist
+        }
+    }
+    __syncthreads();
+    const int r = r0 + warp;                                 // warp i chooses for row i of the block
+    if (warp >= ROUTE_ROWS || r >= rows) return;
     if (row_slot != nullptr && row_slot[r] < 0) {           // a padding row takes no expert
-        for (int c = threadIdx.x; c < top; c += blockDim.x) {
-            choice[(size_t)r * top + c] = -1;
-            weight[(size_t)r * top + c] = 0.0f;
+        if (lane < top) {
+            choice[(size_t)r * top + lane] = -1;
+            weight[(size_t)r * top + lane] = 0.0f;
         }
         return;
     }
-    const T* x = h + (size_t)r * K;
-    // One warp an expert; a lane's share of the sum, and the order of the shares, depend on K alone.
-    const bool wide = K % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)router % 16 == 0;
-    for (int e = warp; e < E; e += warps) {
-        const float* w = router + (size_t)e * K;
-        float z = 0.0f;
-        if (wide) {
-            for (int k = 4 * lane; k < K; k += 128) {
-                const float4 a = route_load4(x + k), b = route_load4(w + k);
-                z = fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, z))));
-            }
-        } else {
-            for (int k = lane; k < K; k += 32) z = fmaf(to_f32(x[k]), w[k], z);
-        }
-        z = warp_sum(z);
-        if (lane == 0) score[e] = z == z ? z : -INFINITY;      // a row of not-a-numbers still chooses experts that exist
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    float* score = score_all + warp * E;
     // Scores from logits; the order of the experts is the order of their logits under either rule.
     float zmax = -INFINITY;
     for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, score[e]);
@@ -91,7 +108,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
         if (best_e == 0x7fffffff) best_e = 0;
         const float s = softmax ? expf(best - zmax) / total : 1.0f / (1.0f + expf(-best));
         picked_sum += s;
-        if (lane == c % 32 && c / 32 == 0) { mine = s; mine_e = best_e; }
+        if (lane == c) { mine = s; mine_e = best_e; }
         __syncwarp();
         if (lane == 0) score[best_e] = INFINITY;
         __syncwarp();
@@ -116,28 +133,80 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ 
     if (threadIdx.x == 0) counts[e] = (int)total;
 }
 
-// One block: where every expert's rows start in sorted order, and the tiles.  table: [0] the number of tiles, then for tile t
-// at 1 + 3 t: expert, first sorted place, rows.
+// One warp: where every expert's rows start in sorted order, and the tiles.  table: [0] the number of tiles, then for tile t
+// at 1 + 3 t: expert, first sorted place, rows.  The lanes take 32 experts at a time and share their sums by shuffles.
+__device__ __forceinline__ void moe_offsets_warp(const int* counts, int E, int* offsets, int* table, int max_tiles, int tile_rows) {
+    const int lane = threadIdx.x & 31;
+    int at = 0, tiles = 0;                                   // the same in every lane
+    for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int n = e < E ? counts[e] : 0;
+        const int t = (n + tile_rows - 1) / tile_rows;
+        int rows_before = n, tiles_before = t;               // inclusive sums over the lanes, then made exclusive
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, rows_before, o), b = __shfl_up_sync(0xffffffffu, tiles_before, o);
+            if (lane >= o) { rows_before += a; tiles_before += b; }
+        }
+        const int all_rows = __shfl_sync(0xffffffffu, rows_before, 31), all_tiles = __shfl_sync(0xffffffffu, tiles_before, 31);
+        rows_before += at - n;
+        tiles_before += tiles - t;
+        if (e < E) {
+            offsets[e] = rows_before;
+            for (int i = 0; i < t && tiles_before + i < max_tiles; i++) {
+                table[1 + 3 * (tiles_before + i)] = e;
+                table[2 + 3 * (tiles_before + i)] = rows_before + i * tile_rows;
+                table[3 + 3 * (tiles_before + i)] = min(tile_rows, n - i * tile_rows);
+            }
+        }
+        at += all_rows;
+        tiles += all_tiles;
+    }
+    if (lane == 0) {
+        offsets[E] = at;
+        table[0] = min(tiles, max_tiles);
+    }
+}
+
 __global__ void __launch_bounds__(32) moe_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ table,
                                                         int max_tiles, int tile_rows) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(counts);
-    if (threadIdx.x != 0) return;
-    int at = 0, tiles = 0;
-    for (int e = 0; e < E; e++) {
-        offsets[e] = at;
-        const int n = counts[e];
-        for (int s = 0; s < n && tiles < max_tiles; s += tile_rows) {
-            table[1 + 3 * tiles] = e;
-            table[2 + 3 * tiles] = at + s;
-            table[3 + 3 * tiles] = min(tile_rows, n - s);
-            tiles++;
-        }
-        at += n;
+    moe_offsets_warp(counts, E, offsets, table, max_tiles, tile_rows);
+}
+
+// Few pairs (a step of single rows): the three kernels of the sort as one block.  A warp an expert counts, then one warp
+// lays out offsets and tiles, then a warp an expert gives its pairs their places, in the order of the pairs as ever.
+__global__ void __launch_bounds__(256) moe_plan_small_kernel(const int* __restrict__ choice, int pairs, int E, int tile_rows, int max_tiles,
+                                                            int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ table,
+                                                            int* __restrict__ perm, int* __restrict__ place) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(choice);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = warp; e < E; e += 8) {
+        int n = 0;
+        for (int i0 = 0; i0 < pairs; i0 += 32) n += __popc(__ballot_sync(0xffffffffu, i0 + lane < pairs && choice[i0 + lane] == e));
+        if (lane == 0) counts[e] = n;
     }
-    offsets[E] = at;
-    table[0] = tiles;
+    __syncthreads();
+    if (warp == 0) moe_offsets_warp(counts, E, offsets, table, max_tiles, tile_rows);
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        int at = offsets[e];
+        for (int i0 = 0; i0 < pairs; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < pairs && choice[i] == e;
+            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int j = at + __popc(ballot & ((1u << lane) - 1u));
+                perm[j] = i;
+                place[i] = j;
+            }
+            at += __popc(ballot);
+        }
+    }
 }
 
 // One block an expert walks the pairs again, in the same order, and gives each of its own the next place.
@@ -316,10 +385,10 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ choice, 
 template <class T>
 static int route(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top, int softmax,
                  int renorm, cudaStream_t s) {
-    BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 8192, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
+    BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 2048, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
     if (rows == 0) return BC_OK;
-    bc_launch(moe_route_kernel<T>, dim3(rows), dim3(256), (size_t)E * sizeof(float), s, (const T*)h, router, row_slot, choice, weight, E, K, top,
-              softmax, renorm);
+    bc_launch(moe_route_kernel<T>, dim3((rows + ROUTE_ROWS - 1) / ROUTE_ROWS), dim3(256), (size_t)ROUTE_ROWS * E * sizeof(float), s, (const T*)h,
+              router, row_slot, choice, weight, rows, E, K, top, softmax, renorm);
     BC_LAUNCH_STATUS();
 }
 // h: [rows, K] of the activation type; router: [E, K] float; row_slot: [rows] (negative: a padding row; may be null);
@@ -342,6 +411,11 @@ extern "C" int bc_moe_plan(const int* choice, int pairs, int E, int tile_rows, i
                            cudaStream_t s) {
     BC_CHECK_ARG(pairs >= 0 && E > 0 && E <= 65535 && tile_rows > 0, "moe_plan: bad sizes pairs=%d E=%d tile_rows=%d", pairs, E, tile_rows);
     if (pairs == 0) return BC_OK;
+    if (pairs <= 1024 && E <= 1024) {      // by the sizes alone
+        bc_launch(moe_plan_small_kernel, dim3(1), dim3(256), 0, s, choice, pairs, E, tile_rows, bc_moe_max_tiles(pairs, E, tile_rows), counts, offsets,
+                  table, perm, place);
+        BC_LAUNCH_STATUS();
+    }
     bc_launch(moe_count_kernel, dim3(E), dim3(256), 0, s, choice, pairs, counts);
     bc_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, E, offsets, table, bc_moe_max_tiles(pairs, E, tile_rows), tile_rows);
     bc_launch(moe_fill_kernel, dim3(E), dim3(256), 0, s, choice, pairs, (const int*)offsets, perm, place);
