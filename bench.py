@@ -661,7 +661,10 @@ def pozirax_costs(c, layers, batch, ctx_len, T) -> dict:
         "rotary + append": np_ * B * 6.0 * n_qkv,
         "attention": np_ * B * (seen_decode * G * (D + DV) * 2.0 + 2.0 * H * (D + DV)),
         "output product": ng * (2.0 * Hg * Pg * E + B * (2.0 * Hg * Pg + 8.0 * E)) + np_ * (2.0 * (H * DV + inner) * E + B * (2.0 * (H * DV + inner) + 16.0 * E)),
-        "routing": layers * (4.0 * X * E + B * (2.0 * E + 8.0 * k) + B * k * E * 4.0 + B * E * 8.0),
+        "routing": layers * (4.0 * X * E + B * (2.0 * E + 8.0 * k)),
+        "expert sort": layers * B * k * 16.0,
+        "expert gather": layers * B * k * E * 4.0,
+        "expert sum": layers * (B * k * E * 4.0 + B * E * 8.0),
         "expert product": layers * (touched * 3.0 * f * E * 2.0 + B * k * (2.0 * E + 4.0 * f + 4.0 * E)),
         "gate/up product": layers * (4.0 * fs * E + B * (2.0 * E + 2.0 * fs)),
         "down product": layers * (2.0 * fs * E + B * (2.0 * fs + 8.0 * E)),
@@ -678,7 +681,10 @@ def pozirax_costs(c, layers, batch, ctx_len, T) -> dict:
         "rotary + append": ("bytes", np_ * T * 6.0 * n_qkv),
         "attention": ("flops", np_ * 2.0 * H * (D + DV) * seen_prefill),
         "output product": ("flops", 2.0 * T * E * (ng * Hg * Pg + np_ * (H * DV + inner))),
-        "routing": ("bytes", layers * T * (2.0 * E + 8.0 * k + k * E * 4.0 + E * 8.0)),
+        "routing": ("flops32", layers * 2.0 * T * X * E),
+        "expert sort": ("bytes", layers * T * k * 16.0),
+        "expert gather": ("bytes", layers * T * k * E * 4.0),
+        "expert sum": ("bytes", layers * T * (k * E * 4.0 + E * 8.0)),
         "expert product": ("flops", layers * 2.0 * T * k * 3.0 * f * E),
         "gate/up product": ("flops", layers * 4.0 * T * fs * E),
         "down product": ("flops", layers * 2.0 * T * fs * E),

@@ -1122,7 +1122,7 @@ static int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, TcGroupP
 
 // X [rows, K] bf16, sorted by matrix; W [matrices, N, K] bf16 (gated: [matrices, 2 N, K], gate rows then up rows); out
 // [rows, N]: bf16 silu(gate) * up if gated, else float.  table: [0] tiles; then, a tile, matrix, first row, rows (at most
-// tile_rows, one of 16, 32, 64, 128); max_tiles: the most tiles the table can hold.  K a multiple of 8.
+// tile_rows, one of 16, 32, 64, 128, 256); max_tiles: the most tiles the table can hold.  K a multiple of 8.
 extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, const int* table, int rows, int matrices, int N, int K, int gated,
                                        int tile_rows, int max_tiles, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && matrices > 0 && N > 0 && K > 0, "gemm_tc_grouped: bad sizes rows=%d matrices=%d N=%d K=%d", rows, matrices, N, K);
@@ -1148,7 +1148,7 @@ extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, 
     case BN:                                                                                \
         return gated ? launch_grouped<BN, EPI_SWIGLU>(mw, mx, p, max_tiles, s) : launch_grouped<BN, EPI_STORE_F32>(mw, mx, p, max_tiles, s);
     switch (tile_rows) {
-        GROUPED(16) GROUPED(32) GROUPED(64) GROUPED(128)
+        GROUPED(16) GROUPED(32) GROUPED(64) GROUPED(128) GROUPED(256)
     }
 #undef GROUPED
     bc_set_error("gemm_tc_grouped: no kernel for tiles of %d rows", tile_rows);

@@ -362,7 +362,8 @@ gla_decay_kernel(const float* __restrict__ proj, int stride, int inner_at, const
     __syncthreads();
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float z = b[c];
-        for (int i = 0; i < rank; i++) z = fmaf(w2t[(size_t)i * W + c], inner[i], z);
+#pragma unroll 8
+        for (int i = 0; i < rank; i++) z = fmaf(w2t[(size_t)i * W + c], inner[i], z);      // eight loads asked for together; the sum's order stays
         const float m = -z;                                          // softplus(m) = max(m, 0) + log1p(exp(-|m|))
         const float sp = fmaxf(m, 0.0f) + log1pf(expf(-fabsf(m)));
         decay[(size_t)r * W + c] = expf(-sp * inv_tau);

@@ -28,51 +28,61 @@ __device__ __forceinline__ float4 route_load4(const bf16* p) {
     return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
 }
 
-#define ROUTE_ROWS 4        // rows a block: every expert's weights are read once for four rows
+#define ROUTE_ROWS 4        // rows a block: an expert's weights are read once for four rows
+#define ROUTE_EXPERTS 8     // experts a block, one a warp
 
+// logits[r][e] = router[e] . h[r] in float.  Block (x, y): rows 4 x .. and experts 8 y ..; a lane's share of a row's sum,
+// and the order of the shares, depend on K alone, so a row's logits are the same bits in any batch.
 template <class T>
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const int* __restrict__ row_slot, int* __restrict__ choice,
-                 float* __restrict__ weight, int rows, int E, int K, int top, int softmax, int renorm) {
-    extern __shared__ float score_all[];                    // [ROUTE_ROWS][E]
+__global__ void __launch_bounds__(32 * ROUTE_EXPERTS)
+moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ router, float* __restrict__ logits, int rows, int E, int K) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(h);
     const int r0 = blockIdx.x * ROUTE_ROWS;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    // One warp an expert, four rows at a time; a lane's share of a row's sum, and the order of the shares, depend on K alone.
+    const int lane = threadIdx.x & 31, e = blockIdx.y * ROUTE_EXPERTS + (threadIdx.x >> 5);
+    if (e >= E) return;
     const bool wide = K % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)router % 16 == 0;
     const T* x[ROUTE_ROWS];
 #pragma unroll
     for (int i = 0; i < ROUTE_ROWS; i++) x[i] = h + (size_t)min(r0 + i, rows - 1) * K;
-    for (int e = warp; e < E; e += warps) {
-        const float* w = router + (size_t)e * K;
-        float z[ROUTE_ROWS] = {};
-        if (wide) {
-            for (int k = 4 * lane; k < K; k += 128) {
-                const float4 b = route_load4(w + k);
+    const float* w = router + (size_t)e * K;
+    float z[ROUTE_ROWS] = {};
+    if (wide) {
+#pragma unroll 4
+        for (int k = 4 * lane; k < K; k += 128) {           // four turns' loads are asked for together
+            const float4 b = route_load4(w + k);
 #pragma unroll
-                for (int i = 0; i < ROUTE_ROWS; i++) {
-                    const float4 a = route_load4(x[i] + k);
-                    z[i] = fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, z[i]))));
-                }
-            }
-        } else {
-            for (int k = lane; k < K; k += 32) {
-                const float b = w[k];
-#pragma unroll
-                for (int i = 0; i < ROUTE_ROWS; i++) z[i] = fmaf(to_f32(x[i][k]), b, z[i]);
+            for (int i = 0; i < ROUTE_ROWS; i++) {
+                const float4 a = route_load4(x[i] + k);
+                z[i] = fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, z[i]))));
             }
         }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float b = w[k];
 #pragma unroll
-        for (int i = 0; i < ROUTE_ROWS; i++) {
-            const float v = warp_sum(z[i]);
-            if (lane == 0) score_all[i * E + e] = v == v ? v : -INFINITY;      // a row of not-a-numbers still chooses experts that exist
+            for (int i = 0; i < ROUTE_ROWS; i++) z[i] = fmaf(to_f32(x[i][k]), b, z[i]);
         }
     }
-    __syncthreads();
-    const int r = r0 + warp;                                 // warp i chooses for row i of the block
-    if (warp >= ROUTE_ROWS || r >= rows) return;
+#pragma unroll
+    for (int i = 0; i < ROUTE_ROWS; i++) {
+        const float v = warp_sum(z[i]);
+        if (lane == 0 && r0 + i < rows) logits[(size_t)(r0 + i) * E + e] = v;
+    }
+}
+
+// One warp a row: the `top` largest logits (the lower index wins a tie) and their scores.
+__global__ void __launch_bounds__(128)
+moe_choose_kernel(const float* __restrict__ logits, const int* __restrict__ row_slot, int* __restrict__ choice, float* __restrict__ weight, int rows,
+                  int E, int top, int softmax, int renorm) {
+    extern __shared__ float score_all[];                    // [4][E]
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(logits);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= rows) return;
     if (row_slot != nullptr && row_slot[r] < 0) {           // a padding row takes no expert
         if (lane < top) {
             choice[(size_t)r * top + lane] = -1;
@@ -81,6 +91,11 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
         return;
     }
     float* score = score_all + warp * E;
+    for (int e = lane; e < E; e += 32) {
+        const float v = logits[(size_t)r * E + e];
+        score[e] = v == v ? v : -INFINITY;                  // a row of not-a-numbers still chooses experts that exist
+    }
+    __syncwarp();
     // Scores from logits; the order of the experts is the order of their logits under either rule.
     float zmax = -INFINITY;
     for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, score[e]);
@@ -364,45 +379,75 @@ moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ perm, const i
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ choice, const int* __restrict__ place, const float* __restrict__ weight,
                    float* __restrict__ residual, int E, int top, int weight_on_output) {
+    __shared__ int where[MOE_MAX_TOP];
+    __shared__ float factor[MOE_MAX_TOP];
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(y); PDL_FRESH(choice); PDL_FRESH(place); PDL_FRESH(weight);
     const int r = blockIdx.x;
+    // The row's places first, so that the loads of a column's values do not each wait for one.
+    if ((int)threadIdx.x < top) {
+        const bool chosen = choice[(size_t)r * top + threadIdx.x] >= 0;
+        where[threadIdx.x] = chosen ? place[(size_t)r * top + threadIdx.x] : -1;
+        factor[threadIdx.x] = weight_on_output ? weight[(size_t)r * top + threadIdx.x] : 1.0f;
+    }
+    __syncthreads();
+    bool any = false;
+    for (int i = 0; i < top; i++) any = any || where[i] >= 0;
+    if (!any) return;
+    if (E % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)residual % 16 == 0) {
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+            for (int i = 0; i < top; i++) {
+                if (where[i] < 0) continue;
+                const float4 v = *reinterpret_cast<const float4*>(y + (size_t)where[i] * E + c);
+                const float f = factor[i];
+                sum = weight_on_output ? make_float4(fmaf(f, v.x, sum.x), fmaf(f, v.y, sum.y), fmaf(f, v.z, sum.z), fmaf(f, v.w, sum.w))
+                                       : make_float4(sum.x + v.x, sum.y + v.y, sum.z + v.z, sum.w + v.w);
+            }
+            float4* out = reinterpret_cast<float4*>(residual + (size_t)r * E + c);
+            const float4 old = *out;
+            *out = make_float4(old.x + sum.x, old.y + sum.y, old.z + sum.z, old.w + sum.w);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < E; c += blockDim.x) {
         float sum = 0.0f;
-        bool any = false;
+#pragma unroll 4
         for (int i = 0; i < top; i++) {
-            if (choice[(size_t)r * top + i] < 0) continue;
-            const float v = y[(size_t)place[(size_t)r * top + i] * E + c];
-            sum = weight_on_output ? fmaf(weight[(size_t)r * top + i], v, sum) : sum + v;
-            any = true;
+            if (where[i] < 0) continue;
+            const float v = y[(size_t)where[i] * E + c];
+            sum = weight_on_output ? fmaf(factor[i], v, sum) : sum + v;
         }
-        if (any) residual[(size_t)r * E + c] += sum;
+        residual[(size_t)r * E + c] += sum;
     }
 }
 
 // ------------------------------------------------------------------------------------ launchers
 template <class T>
-static int route(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top, int softmax,
-                 int renorm, cudaStream_t s) {
+static int route(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E, int K, int top,
+                 int softmax, int renorm, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 2048, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
     if (rows == 0) return BC_OK;
-    bc_launch(moe_route_kernel<T>, dim3((rows + ROUTE_ROWS - 1) / ROUTE_ROWS), dim3(256), (size_t)ROUTE_ROWS * E * sizeof(float), s, (const T*)h,
-              router, row_slot, choice, weight, rows, E, K, top, softmax, renorm);
+    const int groups = (E + ROUTE_EXPERTS - 1) / ROUTE_EXPERTS;
+    BC_CHECK_ARG(groups <= 65535, "moe_route: too many experts (%d)", E);
+    bc_launch(moe_logits_kernel<T>, dim3((rows + ROUTE_ROWS - 1) / ROUTE_ROWS, groups), dim3(32 * ROUTE_EXPERTS), 0, s, (const T*)h, router, logits, rows, E, K);
+    bc_launch(moe_choose_kernel, dim3((rows + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), s, (const float*)logits, row_slot, choice, weight, rows,
+              E, top, softmax, renorm);
     BC_LAUNCH_STATUS();
 }
 // h: [rows, K] of the activation type; router: [E, K] float; row_slot: [rows] (negative: a padding row; may be null);
-// choice: [rows, top] int; weight: [rows, top] float.
-extern "C" int bc_moe_route_f32(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top,
-                                int softmax, int renorm, cudaStream_t s) {
-    return route<float>(h, router, row_slot, choice, weight, rows, E, K, top, softmax, renorm, s);
+// logits: [rows, E] float (scratch); choice: [rows, top] int; weight: [rows, top] float.
+extern "C" int bc_moe_route_f32(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E,
+                                int K, int top, int softmax, int renorm, cudaStream_t s) {
+    return route<float>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, s);
 }
-extern "C" int bc_moe_route_bf16(const void* h, const float* router, const int* row_slot, int* choice, float* weight, int rows, int E, int K, int top,
-                                 int softmax, int renorm, cudaStream_t s) {
-    return route<bf16>(h, router, row_slot, choice, weight, rows, E, K, top, softmax, renorm, s);
+extern "C" int bc_moe_route_bf16(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E,
+                                 int K, int top, int softmax, int renorm, cudaStream_t s) {
+    return route<bf16>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, s);
 }
 
-// The most tiles of `tile_rows` sorted rows that `pairs` rows over E experts can make (every expert may end with a part of a tile).
 extern "C" int bc_moe_max_tiles(int pairs, int E, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + E; }
 extern "C" int bc_moe_simt_tile_rows() { return MOE_BM; }
 

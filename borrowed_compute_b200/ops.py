@@ -132,7 +132,7 @@ def _bounds_paged(who: str, rows: int, row_pos: torch.Tensor, row_slot: torch.Te
 
 
 launches = 0   # kernels launched through this module since import (a captured graph replays them uncounted)
-_KERNELS_PER_CALL = {"bc_argmax": 2, "bc_moe_plan": 3}   # launchers that start more than one kernel
+_KERNELS_PER_CALL = {"bc_argmax": 2, "bc_moe_plan": 3, "bc_moe_route_f32": 2, "bc_moe_route_bf16": 2}   # launchers that start more than one kernel
 
 
 # Timing of single launches, for engine.profile.StepProfile: while `timeline` is a list every
@@ -145,7 +145,8 @@ _CLASS_OF = {
     "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
     "bc_short_conv": "short convolution", "bc_norm_pair": "norm", "bc_delta": "delta rule", "bc_polynorm": "activation", "bc_qkv_prepare": "rotary + append",
     "bc_linear_scan": "recurrence", "bc_ssd_prepare": "recurrence set-up", "bc_gla_decay": "recurrence set-up", "bc_gated_norm": "gated norm",
-    "bc_moe_product": "expert product", "bc_gemm_tc_grouped": "expert product", "bc_moe": "routing", "bc_softcap": "softcap", "bc_reentry": "re-entry",
+    "bc_moe_product": "expert product", "bc_gemm_tc_grouped": "expert product", "bc_moe_route": "routing", "bc_moe_plan": "expert sort",
+    "bc_moe_gather": "expert gather", "bc_moe_combine": "expert sum", "bc_softcap": "softcap", "bc_reentry": "re-entry",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
 }
 
@@ -879,22 +880,23 @@ def gated_norm(y: torch.Tensor, gate: torch.Tensor, gate_at: int, weight: torch.
 
 # ------------------------------------------------------------------------------ routed experts
 
-def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
-              softmax: bool = False, renorm: bool = False) -> None:
+def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Tensor], logits: torch.Tensor, choice: torch.Tensor,
+              weight: torch.Tensor, softmax: bool = False, renorm: bool = False) -> None:
     """choice [rows, top] (int32), weight [rows, top] (float32): every row's ``top`` experts by score, the lower index winning a tie.
     Scores are sigmoid(router @ h) (or a softmax over the experts), computed in float32; weights are the chosen scores, divided by
-    their sum with ``renorm``.  Rows whose slot is negative choose nothing (-1)."""
+    their sum with ``renorm``.  Rows whose slot is negative choose nothing (-1).  ``logits`` [rows, experts] float32 receives router @ h."""
     _need(h, "h")
     _need(router, "router", torch.float32)
+    _need(logits, "logits", torch.float32)
     _need(choice, "choice", torch.int32)
     _need(weight, "weight", torch.float32)
     rows, K = h.shape
     E, top = router.shape[0], choice.shape[1]
-    if router.shape[1] != K or tuple(choice.shape) != (rows, top) or weight.shape != choice.shape:
+    if router.shape[1] != K or tuple(choice.shape) != (rows, top) or weight.shape != choice.shape or tuple(logits.shape) != (rows, E):
         raise KernelError(f"moe_route: h {tuple(h.shape)}, router {tuple(router.shape)}, choice {tuple(choice.shape)} do not fit")
     if row_slot is not None:
         _need(row_slot, "row_slot", torch.int32)
-    _call(_fn("bc_moe_route_" + _suffix(h.dtype)), _ptr(h), _ptr(router), _ptr(row_slot), _ptr(choice), _ptr(weight), _c_int(rows), _c_int(E),
+    _call(_fn("bc_moe_route_" + _suffix(h.dtype)), _ptr(h), _ptr(router), _ptr(row_slot), _ptr(logits), _ptr(choice), _ptr(weight), _c_int(rows), _c_int(E),
           _c_int(K), _c_int(top), _c_int(1 if softmax else 0), _c_int(1 if renorm else 0), _stream())
 
 
@@ -939,7 +941,7 @@ def moe_gather(x: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, weigh
           _c_int(K), _c_int(top), _c_int(1 if weight_on_input else 0), _stream())
 
 
-GROUPED_TILE_ROWS = (16, 32, 64, 128)
+GROUPED_TILE_ROWS = (16, 32, 64, 128, 256)
 
 
 def gemm_tc_grouped_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -1183,13 +1185,15 @@ def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Op
 def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                       seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
                       heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-                      use_tc: Optional[bool] = None, chunk: int = 0, value_dim: Optional[int] = None) -> None:
+                      use_tc: Optional[bool] = None, chunk: int = 0, value_dim: Optional[int] = None, sink: bool = False,
+                      out_scale: float = 1.0) -> None:
     """Causal attention of every sequence's new rows against its cached positions (which
     include the new rows' own keys and values), bf16.  Head sizes 64 and 128 run on the
     tcgen05 tensor cores, 128 query rows a block (scores and output accumulate in TMEM);
     other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other.
     ``chunk`` > 0: a position sees only those of its own chunk of that many positions, counted from position 0.
-    ``value_dim`` (default ``head_dim``): the width of a head's values, in v_cache and in out."""
+    ``value_dim`` (default ``head_dim``): the width of a head's values, in v_cache and in out.
+    ``sink`` adds one to the softmax's denominator (a position of score 0 without a value); ``out_scale`` multiplies the result."""
     value_dim = head_dim if value_dim is None else int(value_dim)
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
@@ -1218,14 +1222,14 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
     if use_tc is None:
         use_tc = attention_prefill_tc_accepts(heads, kv_heads, head_dim, q, q_stride, value_dim)
     if use_tc:
-        _call(_fn("bc_attention_prefill_tc_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+        _call(_fn("bc_attention_prefill_tc_sink_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
               _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads),
               _c_int(head_dim), _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk),
-              _c_float(scale), _stream())
+              _c_float(scale), _c_int(1 if sink else 0), _c_float(out_scale), _stream())
         return
-    if chunk > 0 or value_dim != head_dim:
+    if chunk > 0 or value_dim != head_dim or sink or out_scale != 1.0:
         attention_tiles(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, heads, kv_heads, head_dim,
-                        value_dim, window=window, chunk=chunk, scale=scale)
+                        value_dim, window=window, chunk=chunk, scale=scale, sink=sink, out_scale=out_scale)
         return
     _call(_fn("bc_attention_prefill_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),

@@ -110,13 +110,12 @@ class GroupedQueryAttentionKV(Mixer):
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         H, G, D, DV = self.heads, self.kv_heads, self.head_dim, self.value_dim
-        plain = not self.sink and self.out_scale == 1.0     # the tcgen05 kernel knows neither a sink nor a factor
-        if plain and not force_rows and not force_tiles and not ctx.decode and q.dtype == torch.bfloat16 \
+        if not force_rows and not force_tiles and not ctx.decode and q.dtype == torch.bfloat16 \
                 and ops.attention_prefill_tc_accepts(H, G, D, q, H * D, DV):
             # Prompts with heads of 64 or 128 and values no wider: tcgen05 tiles, scores and output in tensor memory.
             ops.attention_prefill(q, H * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot, ctx.seq_start, out,
                                   ctx.seqs, ctx.max_new, H, G, D, window=self.window, scale=self.scale, use_tc=True, chunk=self.chunk,
-                                  value_dim=DV)
+                                  value_dim=DV, sink=self.sink, out_scale=self.out_scale)
             return
         if not force_rows and ops.attention_tiles_accepts(H, G, D, DV, q.dtype):
             # Tensor-core tiles, for prompts and for single rows alike: the heads of a kv head share every page read.

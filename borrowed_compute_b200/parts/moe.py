@@ -64,7 +64,8 @@ class RoutedExperts(FeedForward):
         i32 = dict(dtype=torch.int32, device=dev)
         choice = torch.empty((rows, top), **i32)
         weight = torch.empty((rows, top), dtype=torch.float32, device=dev)
-        ops.moe_route(x, self.router, ctx.row_slot, choice, weight, softmax=self.softmax, renorm=self.renormalize)
+        logits = torch.empty((rows, E), dtype=torch.float32, device=dev)
+        ops.moe_route(x, self.router, ctx.row_slot, logits, choice, weight, softmax=self.softmax, renorm=self.renormalize)
         # bfloat16 whose widths the tensor cores take: the rows are gathered in sorted order (times their weights: the weight
         # multiplies the expert's input) and both products run on tcgen05 tiles; else on the CUDA cores, gathering as they go.
         tensor_cores = not force_simt and self.intermediate_size % 8 == 0 and ops.gemm_tc_grouped_accepts(x, self.w_gate_up)
