@@ -474,10 +474,30 @@ class Engine:
 
     # ---------------------------------------------------------------------------- accounts
     def weight_bytes(self) -> int:
+        from ..parts.base import Part
+
         seen, total = set(), 0
+
+        def walk(obj) -> None:
+            nonlocal total
+            if isinstance(obj, torch.Tensor):
+                if obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += obj.numel() * obj.element_size()
+            elif isinstance(obj, Part):
+                if id(obj) not in seen:                 # parts inside parts (two mixers side by side, a shared expert) count too
+                    seen.add(id(obj))
+                    for v in vars(obj).values():
+                        walk(v)
+            elif isinstance(obj, dict):
+                for v in obj.values():
+                    if isinstance(v, (Part, torch.Tensor)):
+                        walk(v)
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
+                    if isinstance(v, (Part, torch.Tensor)):
+                        walk(v)
+
         for _, part in self.model.named_parts():
-            for v in vars(part).values():
-                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                    seen.add(v.data_ptr())
-                    total += v.numel() * v.element_size()
+            walk(part)
         return total
