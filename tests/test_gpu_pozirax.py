@@ -518,7 +518,7 @@ def test_long_decoding_and_the_first_tokens():
         close(run_whole(eng, toks[:n]), ref[:n], "float32", f"the first {n}")
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
 def test_drawn_configurations(seed):
     """Sizes drawn at random, among them values that make parts of the design equal or 1."""
     from borrowed_compute_b200.engine import StepEntry
@@ -559,8 +559,70 @@ def test_drawn_configurations(seed):
         out = eng.step([StepEntry(slots[0], [seqs[0][68 + t]], (0,)), StepEntry(slots[2], [seqs[2][129 + t]], (0,))]).cpu().numpy()
         got[0].append(out[:1])
         got[2].append(out[1:])
+    refs = [pp.forward(cfg, w, q) for q in seqs]
     for i in range(3):
-        close(np.concatenate(got[i]), pp.forward(cfg, w, seqs[i]), "float32", f"{json.dumps(cfg)}: sequence {i}")
+        close(np.concatenate(got[i]), refs[i], "float32", f"{json.dumps(cfg)}: sequence {i}")
+    # The same sizes on the bfloat16 kernels: a router's choice may flip by rounding on a few rows (and, through a state,
+    # on those after them), so most rows are held to the oracle, and all of them to being numbers.
+    eng16 = engine_for(cfg, w, "bfloat16", max_tokens=1024, max_slots=4, max_seq=256)
+    for i in (0, 2):
+        got16 = run_cut(eng16, seqs[i], [first[i]])
+        assert np.isfinite(got16).all()
+        errors = np.abs(got16 - refs[i]).max(axis=-1)
+        assert np.median(errors) <= tol("bfloat16", refs[i]), f"{json.dumps(cfg)}: sequence {i} in bfloat16, median error {np.median(errors):.3g}"
+
+
+def test_the_trace_tool_replays_prompts_decoding_and_a_batch(tmp_path):
+    """bin/trace_run on a folder of this design: whole prompts, single tokens after a prompt, and a batch of unequal
+    requests that start together and end one after another, in float32 against the plain implementation."""
+    import subprocess
+    import sys
+
+    from borrowed_compute_b200.weights.safetensors_io import write_safetensors
+    from conftest import ROOT
+
+    cfg = {"architecture": "Pozirax", "vocab": 301, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 7.0}, "logit_softcap": 25.0,
+           "loop": {"start": 1, "stop": 4, "times": 2},
+           "layers": [
+               {"type": "parallel", "mixer": pp._pair(8, 2, 32, 32, 100, 32, 1e5, 0.2, 8, 16, 16, 4, 2, 4, 0.8, 1.2), "mlp": pp._moe(8, 2, 32, 64)},
+               {"type": "gla", "mixer": pp._gla(2, 64, 64, 12.0, 8), "mlp": pp._moe(8, 2, 32, 64)},
+               {"type": "gla", "mixer": pp._gla(4, 16, 48, 6.0, 8), "mlp": None},
+               {"type": "parallel", "mixer": pp._pair(4, 4, 64, 64, 33, 64, 1e4, 0.15, 4, 32, 24, 1, 4, 3, 1.0, 0.6), "mlp": pp._moe(6, 1, 40, 0)},
+               {"type": "gla", "mixer": pp._gla(1, 128, 32, 3.0, 16), "mlp": pp._moe(4, 4, 24, 24)},
+           ]}
+    w = pp.make_weights(cfg, 31)
+    on_disk = copy.deepcopy(cfg)
+    for layer in on_disk["layers"]:
+        layer["mixer"].pop("rank", None)
+    folder, out = str(tmp_path / "model"), str(tmp_path / "out")
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(on_disk, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), {n: torch.from_numpy(a).to(torch.bfloat16) for n, a in w.items()})
+    a, b, c = (tokens_for(70 + i, n, cfg["vocab"]) for i, n in enumerate([150, 40, 9]))
+    refs = {"a": pp.forward(cfg, w, a), "b": pp.forward(cfg, w, b), "c": pp.forward(cfg, w, c)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:120], "want": [0, 64, 119]}], "end": []}]
+    steps += [{"step": 1 + i, "entries": [{"id": "a", "tokens": [a[120 + i]], "want": [0]}], "end": ["a"] if i == 29 else []} for i in range(30)]
+    steps.append({"step": 31, "entries": [{"id": "x", "tokens": a[:100], "want": [99]}, {"id": "y", "tokens": b[:30], "want": []},
+                                          {"id": "z", "tokens": c[:5], "want": [4]}], "end": []})
+    for i in range(10):
+        live = [("x", a, 100), ("y", b, 30)] + ([("z", c, 5)] if i < 4 else [])
+        steps.append({"step": 32 + i, "entries": [{"id": n, "tokens": [t[at + i]], "want": [0]} for n, t, at in live],
+                      "end": (["z"] if i == 3 else []) + (["x", "y"] if i == 9 else [])})
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out,
+                          "--max-tokens", "512"], input=text, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert [line for line in res.stdout.splitlines() if line.startswith("done")] == [f"done {s['step']}" for s in steps]
+    V = cfg["vocab"]
+    read = lambda n: np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V)      # noqa: E731
+    close(read(0), refs["a"][[0, 64, 119]], "float32", "the prompt")
+    for i in range(30):
+        close(read(1 + i), refs["a"][120 + i:121 + i], "float32", f"token {i} after the prompt")
+    close(read(31), np.stack([refs["a"][99], refs["c"][4]]), "float32", "the batch's prompts")
+    for i in range(10):
+        want = [refs["a"][100 + i], refs["b"][30 + i]] + ([refs["c"][5 + i]] if i < 4 else [])
+        close(read(32 + i), np.stack(want), "float32", f"the batch's token {i}")
 
 
 def test_greedy_generation_through_the_entry_point(tmp_path):
