@@ -384,15 +384,17 @@ def test_norm_of_single_heads_and_rotation_of_neighbours(D, rot, pairing):
         close(got_v.reshape(n, -1), x[:, (H + G) * D:], dtype, "v")
 
 
-@pytest.mark.parametrize("E,top,ff,K", [(5, 2, 24, 40), (3, 3, 8, 16), (9, 1, 70, 72), (33, 4, 16, 24)])
-def test_routed_experts(E, top, ff, K):
+@pytest.mark.parametrize("E,top,ff,K,rows", [(5, 2, 24, 40, 77), (3, 3, 8, 16, 77), (9, 1, 70, 72, 77), (33, 4, 16, 24, 77), (5, 2, 16, 32, 150),
+                                             (4, 2, 24, 40, 230), (3, 2, 24, 40, 600)])
+def test_routed_experts(E, top, ff, K, rows):
     """The router's choices (ties to the lower index), the sort by expert, both products and the sum, against the
-    plain loop; rows of no sequence choose nothing and change nothing."""
+    plain loop; rows of no sequence choose nothing.  The rows an expert gets on average decide the tile of the
+    tensor-core products: the cases reach tiles of 16, 32, 64, 128 and 256 sorted rows, and widths that only the
+    CUDA-core products take."""
     from borrowed_compute_b200.parts.base import Runtime, StepContext
     from borrowed_compute_b200.parts.moe import RoutedExperts
 
     rng = np.random.default_rng(E)
-    rows = 77
     w = {"router": pp.bf16_round(rng.standard_normal((E, K)))}
     for e in range(E):
         w.update({f"e{e}.gate": pp.bf16_round(rng.standard_normal((ff, K)) / math.sqrt(K)), f"e{e}.up": pp.bf16_round(rng.standard_normal((ff, K)) / math.sqrt(K)),
