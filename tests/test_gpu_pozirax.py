@@ -426,6 +426,33 @@ def test_routed_experts(E, top, ff, K, rows):
             assert torch.equal(alone[0], residual[40])
 
 
+def test_scaled_embedding_soft_cap_and_the_mix_with_the_embedding():
+    from borrowed_compute_b200 import ops
+    from borrowed_compute_b200.parts.base import Runtime
+    from borrowed_compute_b200.parts.reentry import MixWithEmbedding
+
+    rng = np.random.default_rng(3)
+    V, E, rows = 37, 40, 11
+    table = pp.bf16_round(rng.standard_normal((V, E)))
+    toks = rng.integers(0, V, rows)
+    for dtype, td in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        out = torch.empty((rows, E), dtype=torch.float32, device=DEV)
+        ops.embed(dev(table, td), i32(toks), out, 6.5)
+        assert np.array_equal(out.cpu().numpy(), table[toks] * np.float32(6.5))
+        x, x0 = rng.standard_normal((rows, E)).astype(np.float32), rng.standard_normal((rows, E)).astype(np.float32)
+        w_in, steps = pp.bf16_round(rng.standard_normal((E, 2 * E)) / 6), pp.bf16_round(rng.standard_normal((3, E)))
+        part = MixWithEmbedding(E, 3)
+        part.load({"in": dev(w_in, td), "step": dev(steps)}, Runtime(torch.device(DEV), td))
+        for number in (0, 2):
+            stream = dev(x)
+            part.forward(stream, dev(x0), None, number)
+            close(stream.cpu().numpy(), np.concatenate([pp.f64(x), pp.f64(x0)], axis=1) @ pp.f64(w_in).T + steps[number], dtype, f"pass {number}")
+    scores = rng.standard_normal((5, 23)).astype(np.float32) * 40
+    capped = dev(scores)
+    ops.softcap(capped, 15.0)
+    close(capped.cpu().numpy(), 15.0 * np.tanh(pp.f64(scores) / 15.0), "float32", "soft cap")
+
+
 # ---------------------------------------------------------------------------- whole models
 
 @pytest.mark.parametrize("name", ["A", "B"])
