@@ -62,7 +62,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
                         int n_pages, int window, float scale_log2, const float2* __restrict__ cos_sin, int pairing, int fuse,
-                        int k_off, int v_off, bf16* __restrict__ k_write, bf16* __restrict__ v_write, int use_cluster) {
+                        int k_off, int v_off, bf16* __restrict__ k_write, bf16* __restrict__ v_write, int use_cluster, int sink,
+                        float out_scale) {
     constexpr int CHUNKS = D / 8;              // 16-byte chunks a row
     constexpr int TILE_BYTES = 64 * D * 2;     // one page of one kv head
     constexpr int KD = D / 16;                 // k-steps of Q K^T
@@ -430,7 +431,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         const int h = g * group + hr;
         if (n_splits == 1) {
-            out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            // A sink is one more position of score 0 that has no value: it adds 2^(0 - M) to the sum of the weights alone, once,
+            // where a row's last sums are made (here and at the two merges below).
+            if (sink && M != -INFINITY) L += exp2f(-M);
+            out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O * out_scale / L : 0.0f);
         } else if (use_cluster) {
             po[i] = O;
             if (d == 0) {
@@ -492,7 +496,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     O += os[sp] * f;
                 }
                 if (parts == 1) {
-                    out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+                    if (sink && M != -INFINITY) L += exp2f(-M);
+                    out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O * out_scale / L : 0.0f);
                 } else {
                     float* dst = scratch + (((size_t)r * H + g * group + hr) * parts + part) * stride;
                     __stcg(dst + d, O);
@@ -536,7 +541,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             L += __ldcg(src + (size_t)sp * stride + D + 1) * f;
             O += __ldcg(src + (size_t)sp * stride + d) * f;
         }
-        out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        if (sink && M != -INFINITY) L += exp2f(-M);
+        out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O * out_scale / L : 0.0f);
     }
 }
 
@@ -546,6 +552,8 @@ struct FusedRope {
     int fuse;               // 0: q is already rotated and the cache already holds the row; 1: rotate q; 2: rotate q and append k, v
     int k_off, v_off;       // where a row's k and v heads start inside the fused projection, in elements
     bool allow_cluster;     // splits may run as a thread-block cluster (else they go through scratch memory)
+    int sink;               // 1: one added to the softmax's denominator (a position of score 0 without a value)
+    float out_scale;        // a factor on the result
 };
 
 // Whether pages come by TMA where the head size allows (the default) or by cp.async
@@ -608,12 +616,12 @@ static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
         bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(TMA ? AD_THREADS_TMA : AD_THREADS), (size_t)SMEM, s, dim3(csize, 1, 1), mk, mv, (const bf16*)q,
                             q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
                             max_pages, n_pages, window, scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse,
-                            fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, csize);
+                            fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, csize, fr.sink, fr.out_scale);
     else
         bc_launch(attention_decode_kernel<D, TMA>, grid, dim3(TMA ? AD_THREADS_TMA : AD_THREADS), (size_t)SMEM, s, mk, mv, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
                   scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
-                  (bf16*)v_cache, 0);
+                  (bf16*)v_cache, 0, fr.sink, fr.out_scale);
     BC_LAUNCH_STATUS();
 }
 
@@ -656,10 +664,10 @@ extern "C" int bc_attention_decode_workspace(int rows, int H, int G, int D, int 
 // before attending; fuse = 0 is the plain kernel.  cos_sin [positions, D/2, 2] float, or
 // null for no rotation.  Two to eight splits run as a thread-block cluster and need no
 // scratch memory; adding 4 to fuse sends them through scratch memory like larger counts.
-extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
-                                              const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows,
-                                              int H, int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits,
-                                              const float* cos_sin, int pairing, int fuse, cudaStream_t s) {
+static int decode_fused(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
+                        const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int D, int max_pages, int n_pages,
+                        int window, float scale, int n_splits, const float* cos_sin, int pairing, int fuse, int sink, float out_scale,
+                        cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && rows <= 65535, "attention_decode: %d rows (at most 65535)", rows);
     BC_CHECK_ARG(bc_attention_decode_accepts(H, G, D), "attention_decode: H=%d G=%d D=%d is outside what this kernel takes "
                  "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AD_MAX_GROUP);
@@ -670,7 +678,7 @@ extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const
     BC_CHECK_ARG((fuse & 3) == 0 || q_stride == (H + 2 * G) * D, "attention_decode: fused mode wants the fused projection, stride %d", (H + 2 * G) * D);
     BC_CHECK_ARG((fuse & 3) == 0 || cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0, "attention_decode: the rotary table must be 16-byte aligned");
     if (rows == 0) return BC_OK;
-    FusedRope fr{cos_sin, pairing, fuse & 3, H * D, (H + G) * D, (fuse & 4) == 0};
+    FusedRope fr{cos_sin, pairing, fuse & 3, H * D, (H + G) * D, (fuse & 4) == 0, sink, out_scale};
 #define AD_CASE(DD) \
     case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages, n_pages, window, scale, n_splits, fr, s);
     switch (D) {
@@ -679,6 +687,25 @@ extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const
 #undef AD_CASE
     bc_set_error("attention_decode: no kernel for head size %d", D);
     return BC_ERR_ARG;
+}
+
+extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                              const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows,
+                                              int H, int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits,
+                                              const float* cos_sin, int pairing, int fuse, cudaStream_t s) {
+    return decode_fused(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, D, max_pages, n_pages, window,
+                        scale, n_splits, cos_sin, pairing, fuse, 0, 1.0f, s);
+}
+
+// The plain kernel (q rotated already, the cache holding the row) with a sink (one more position of score 0 without a value,
+// counted once where a row's last sums are made) and a factor on the output; fuse: 0, or 4 to send the splits through scratch.
+extern "C" int bc_attention_decode_sink_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                             const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows,
+                                             int H, int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits, int fuse,
+                                             int sink, float out_scale, cudaStream_t s) {
+    BC_CHECK_ARG((fuse & 3) == 0, "attention_decode: the sink comes with the plain kernel (fuse %d)", fuse);
+    return decode_fused(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, D, max_pages, n_pages, window,
+                        scale, n_splits, nullptr, 0, fuse, sink, out_scale, s);
 }
 
 // q: row r's head h at q + r * q_stride + h * D.  scratch / counters: see above; counters
@@ -733,7 +760,7 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
     }
     bc_launch(attention_decode_kernel<D, false>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, none, none, (const bf16*)q, q_stride,
               (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages,
-              n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr, 0);
+              n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr, 0, 0, 1.0f);
     BC_LAUNCH_STATUS();
 }
 

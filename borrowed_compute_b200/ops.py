@@ -1084,7 +1084,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
                      row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                      window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None, fuse: int = 0,
                      cos_sin: Optional[torch.Tensor] = None, pairing: int = 0, via_scratch: bool = False,
-                     reach: Optional[int] = None) -> None:
+                     reach: Optional[int] = None, sink: bool = False, out_scale: float = 1.0) -> None:
     """Attention of one new row a sequence (bf16): the cached positions are split across
     blocks and the heads of a kv head share each read; results are merged in a fixed order.
     Two to eight splits form a thread-block cluster and merge through one another's shared
@@ -1093,7 +1093,9 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
     the fly by ``cos_sin`` (None: no rotation), and with 2 the row's rotated key and its
     value are appended to the cache first (what rope_append would have done).  ``reach``:
     a bound on the positions any row reaches (else what the page table can hold); the
-    number of splits is chosen by it, no result depends on it."""
+    number of splits is chosen by it, no result depends on it.  ``sink`` adds one to the softmax's
+    denominator (a position of score 0 without a value), ``out_scale`` multiplies the result: both
+    with the plain kernel (``fuse`` 0) only."""
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -1125,6 +1127,14 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
         if bounds_check and not torch.cuda.is_current_stream_capturing():
             _bounds("attention_decode: row_pos (against the rotary table)", row_pos.reshape(-1)[:rows][row_slot.reshape(-1)[:rows] >= 0], cos_sin.shape[0])
     _bounds_paged("attention_decode", rows, row_pos, row_slot, page_table, k_cache.shape[0])
+    if sink or out_scale != 1.0:
+        if fuse != 0:
+            raise KernelError("attention_decode: a sink or a factor comes with the plain kernel (fuse 0)")
+        _call(_fn("bc_attention_decode_sink_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
+              _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+              _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits),
+              _c_int(4 if via_scratch else 0), _c_int(1 if sink else 0), _c_float(out_scale), _stream())
+        return
     _call(_fn("bc_attention_decode_fused_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
           _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _ptr(cos_sin),

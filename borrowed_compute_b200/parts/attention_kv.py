@@ -117,6 +117,11 @@ class GroupedQueryAttentionKV(Mixer):
                                   ctx.seqs, ctx.max_new, H, G, D, window=self.window, scale=self.scale, use_tc=True, chunk=self.chunk,
                                   value_dim=DV, sink=self.sink, out_scale=self.out_scale)
             return
+        if not force_rows and not force_tiles and ctx.decode and D == DV and self.chunk == 0 and ops.attention_decode_accepts(H, G, D, q.dtype):
+            # Single rows over keys and values of one width, no chunk mask: the kernel that splits a row's positions over blocks.
+            ops.attention_decode(q, H * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out, H, G, D, window=self.window,
+                                 scale=self.scale, reach=ctx.max_total, sink=self.sink, out_scale=self.out_scale)
+            return
         if not force_rows and ops.attention_tiles_accepts(H, G, D, DV, q.dtype):
             # Tensor-core tiles, for prompts and for single rows alike: the heads of a kv head share every page read.
             ops.attention_tiles(q, H * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot, ctx.seq_start, out,

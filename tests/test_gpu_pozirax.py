@@ -296,7 +296,11 @@ def run_attention(q, k, v, window, scale, dtype, cuts, kernel, H, G, D, DV, sink
         q_out = torch.empty((n, H * D), dtype=td, device=DEV)
         ops.qkv_prepare_heads(qkv, None, None, None, i32(pos), i32([1] * n), table, q_out, k_cache, v_cache, H, G, D, DV, 0, 1, 0.0)
         out = torch.empty((n, H * DV), dtype=td, device=DEV)
-        if kernel == "tc" and n > 1:
+        if kernel == "split" and n == 1:
+            for via_scratch in (False, True):                       # the splits' two ways of merging give the same
+                ops.attention_decode(q_out, H * D, k_cache, v_cache, table, i32(pos), i32([1]), out, H, G, D, window=window, scale=scale,
+                                     splits=2 if at >= 64 and window != 1 else 1, via_scratch=via_scratch, sink=sink, out_scale=out_scale)
+        elif kernel == "tc" and n > 1:
             ops.attention_prefill(q_out, H * D, k_cache, v_cache, table, i32([0, n]), i32([1]), i32([at]), out, 1, n, H, G, D, window=window, scale=scale,
                                   use_tc=True, value_dim=DV, sink=sink, out_scale=out_scale)
         elif kernel == "rows":
@@ -310,13 +314,14 @@ def run_attention(q, k, v, window, scale, dtype, cuts, kernel, H, G, D, DV, sink
     return np.concatenate(outs).reshape(T, H, DV)
 
 
-@pytest.mark.parametrize("dtype,kernel", [("float32", "rows"), ("bfloat16", "rows"), ("bfloat16", "tiles"), ("bfloat16", "tc")])
+@pytest.mark.parametrize("dtype,kernel", [("float32", "rows"), ("bfloat16", "rows"), ("bfloat16", "tiles"), ("bfloat16", "tc"), ("bfloat16", "split")])
 @pytest.mark.parametrize("window", [0, 1, 9, 64, 70])
 def test_sink_attention_with_one_key_that_matters_at_every_edge(dtype, kernel, window):
     """A key just inside the window takes nearly all the weight, one just outside none; in a prompt and when the row is
     decoded alone; at a page's border; and a row whose scores are all very low gives nearly nothing (the sink).  The
-    tcgen05 kernel takes prompts of heads of 64 or 128 (single rows go to the tiles there too)."""
-    H, G, D, DV, T, scale = (4, 2, 32, 16, 150, 0.2) if kernel != "tc" else (4, 2, 128, 64, 150, 0.1)
+    tcgen05 kernel takes prompts of heads of 64 or 128 (single rows go to the tiles there too); "split" sends single
+    rows to the kernel that splits a row's positions over blocks (prompts to the tiles)."""
+    H, G, D, DV, T, scale = {"tc": (4, 2, 128, 64, 150, 0.1), "split": (4, 2, 64, 64, 150, 0.15)}.get(kernel, (4, 2, 32, 16, 150, 0.2))
     rng = np.random.default_rng(window)
     row = 140
     edges = [row, row - 1, 128, 127, 0] if window == 0 else sorted({row - window + 1, row - window, max(row - window + 2, 0), row})
