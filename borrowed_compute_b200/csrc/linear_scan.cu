@@ -382,17 +382,22 @@ extern "C" int bc_gla_decay(const float* proj, int stride, int inner_at, const f
 
 // -------------------------------------------------------------------------------- gated_norm
 // y: [rows, W] float; gate: row r's at gate + r * g_stride; weight: `period` values, repeated over the row (period = W: one
-// a column; period = W / parts: shared by the parts).  Block (part, row): z = y (* silu(g) if gate_first); z over the root mean
+// a column; period = W / parts: shared by the parts); row_slot (may be null): rows whose slot is negative give zeros.  Block (part, row): z = y (* silu(g) if gate_first); z over the root mean
 // square of the part, eps inside the root; times weight (times silu(g) if not gate_first); times factor.
 template <class T>
 __global__ void __launch_bounds__(256)
 gated_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int g_stride, const float* __restrict__ weight, int period,
-                  T* __restrict__ out, int W, int part, float eps, int gate_first, float factor) {
+                  const int* __restrict__ row_slot, T* __restrict__ out, int W, int part, float eps, int gate_first, float factor) {
     __shared__ float scratch[32];
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(y); PDL_FRESH(gate);
     const int r = blockIdx.y, c0 = blockIdx.x * part;
+    if (row_slot != nullptr && row_slot[r] < 0) {
+        // A row of no sequence: nothing wrote its y (the recurrence walks sequences), so it is not read; zeros go on.
+        for (int c = threadIdx.x; c < part; c += blockDim.x) out[(size_t)r * W + c0 + c] = from_f32<T>(0.0f);
+        return;
+    }
     const float* yr = y + (size_t)r * W + c0;
     const float* gr = gate + (size_t)r * g_stride + c0;
     float ss = 0.0f;
@@ -415,27 +420,26 @@ gated_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, i
 }
 
 template <class T>
-static int gated_norm(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W, int parts,
-                      float eps, int gate_first, float factor, cudaStream_t s) {
+static int gated_norm(const float* y, const float* gate, int g_stride, const float* weight, int period, const int* row_slot, void* out, int rows,
+                      int W, int parts, float eps, int gate_first, float factor, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && rows <= 2147483647 && W > 0 && parts > 0 && parts <= 65535 && W % parts == 0, "gated_norm: bad sizes rows=%d W=%d parts=%d", rows, W, parts);
     BC_CHECK_ARG(period > 0 && (period == W || period == W / parts), "gated_norm: a weight of %d values fits neither the row nor a part", period);
     if (rows == 0) return BC_OK;
     const int part = W / parts;
     const int threads = part >= 1024 ? 256 : part >= 256 ? 128 : part >= 64 ? 64 : 32;       // by the part's width alone
-    dim3 grid(parts, rows > 65535 ? 65535 : rows);
     // More rows than a grid's second dimension holds go in turns.
     for (int at = 0; at < rows; at += 65535) {
         const int n = rows - at < 65535 ? rows - at : 65535;
         bc_launch(gated_norm_kernel<T>, dim3(parts, n), dim3(threads), 0, s, y + (size_t)at * W, gate + (size_t)at * g_stride, g_stride, weight, period,
-                  (T*)out + (size_t)at * W, W, part, eps, gate_first, factor);
+                  row_slot ? row_slot + at : nullptr, (T*)out + (size_t)at * W, W, part, eps, gate_first, factor);
     }
     BC_LAUNCH_STATUS();
 }
-extern "C" int bc_gated_norm_f32(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W,
-                                 int parts, float eps, int gate_first, float factor, cudaStream_t s) {
-    return gated_norm<float>(y, gate, g_stride, weight, period, out, rows, W, parts, eps, gate_first, factor, s);
+extern "C" int bc_gated_norm_f32(const float* y, const float* gate, int g_stride, const float* weight, int period, const int* row_slot, void* out,
+                                 int rows, int W, int parts, float eps, int gate_first, float factor, cudaStream_t s) {
+    return gated_norm<float>(y, gate, g_stride, weight, period, row_slot, out, rows, W, parts, eps, gate_first, factor, s);
 }
-extern "C" int bc_gated_norm_bf16(const float* y, const float* gate, int g_stride, const float* weight, int period, void* out, int rows, int W,
-                                  int parts, float eps, int gate_first, float factor, cudaStream_t s) {
-    return gated_norm<bf16>(y, gate, g_stride, weight, period, out, rows, W, parts, eps, gate_first, factor, s);
+extern "C" int bc_gated_norm_bf16(const float* y, const float* gate, int g_stride, const float* weight, int period, const int* row_slot, void* out,
+                                  int rows, int W, int parts, float eps, int gate_first, float factor, cudaStream_t s) {
+    return gated_norm<bf16>(y, gate, g_stride, weight, period, row_slot, out, rows, W, parts, eps, gate_first, factor, s);
 }

@@ -862,10 +862,11 @@ def gla_decay(proj: torch.Tensor, inner_at: int, w2t: torch.Tensor, bias: torch.
 
 
 def gated_norm(y: torch.Tensor, gate: torch.Tensor, gate_at: int, weight: torch.Tensor, out: torch.Tensor, parts: int, eps: float,
-               gate_first: bool, factor: float = 1.0) -> None:
+               gate_first: bool, factor: float = 1.0, row_slot: Optional[torch.Tensor] = None) -> None:
     """Every row of y [rows, W] (float32) in ``parts`` equal parts, each divided by its own root mean square and multiplied by
     ``weight`` (as wide as the row, or as a part and then shared by the parts); silu of the gate (columns gate_at .. of ``gate``,
-    float32) multiplies before the norm (``gate_first``) or after it; ``factor`` multiplies the result."""
+    float32) multiplies before the norm (``gate_first``) or after it; ``factor`` multiplies the result.  With ``row_slot``, rows whose
+    slot is negative are not read and give zeros."""
     _need(y, "y", torch.float32)
     _need(gate, "gate", torch.float32)
     _need(weight, "weight", torch.float32)
@@ -873,8 +874,12 @@ def gated_norm(y: torch.Tensor, gate: torch.Tensor, gate_at: int, weight: torch.
     rows, W = y.shape
     if out.shape != y.shape or gate.shape[0] < rows or gate_at + W > gate.shape[1] or W % parts or weight.numel() not in (W, W // parts):
         raise KernelError(f"gated_norm: y {tuple(y.shape)}, gate {tuple(gate.shape)}, weight {weight.numel()}, {parts} parts do not fit")
+    if row_slot is not None:
+        _need(row_slot, "row_slot", torch.int32)
+        if row_slot.numel() < rows:
+            raise KernelError("gated_norm: fewer slots than rows")
     _call(_fn("bc_gated_norm_" + _suffix(out.dtype)), _ptr(y), _c_void_p(gate.data_ptr() + 4 * gate_at), _c_int(gate.shape[1]), _ptr(weight),
-          _c_int(weight.numel()), _ptr(out), _c_int(rows), _c_int(W), _c_int(parts), _c_float(eps), _c_int(1 if gate_first else 0),
+          _c_int(weight.numel()), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(W), _c_int(parts), _c_float(eps), _c_int(1 if gate_first else 0),
           _c_float(factor), _stream())
 
 

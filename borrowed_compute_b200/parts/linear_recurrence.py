@@ -30,13 +30,6 @@ from . import products
 from .base import MIXERS, Mixer, RunMemory, Runtime, StateNeed, StepContext, TensorSpec
 
 
-def _scan_output(rows: int, width: int, ctx: StepContext, device) -> torch.Tensor:
-    """The recurrence writes the rows of live sequences only: where a step may hold rows of no sequence (a captured
-    step's padding, a padded prompt step) the others start as zeros, so that nothing undefined flows on."""
-    padded = ctx.decode or not ctx.host_seq_rows or ctx.host_seq_rows[-1] != rows
-    return (torch.zeros if padded else torch.empty)((rows, width), dtype=torch.float32, device=device)
-
-
 @MIXERS.register("gated_linear_attention")
 class GatedLinearAttention(Mixer):
     def __init__(self, hidden_size: int, heads: int, head_dim: int, value_dim: int, decay_rank: int, tau: float, norm_eps: float,
@@ -78,11 +71,12 @@ class GatedLinearAttention(Mixer):
         products.linear(x, self.w_in, proj, products.EPI_STORE_F32, "recurrence projections")
         decay = torch.empty((rows, hd), dtype=torch.float32, device=dev)
         ops.gla_decay(proj, 2 * hd + 2 * hp, self.a2_t, self.a2_b, decay, self.tau)
-        o = _scan_output(rows, hp, ctx, dev)
+        # The recurrence writes the rows of live sequences only; the norm after it skips the others (rows of no sequence).
+        o = torch.empty((rows, hp), dtype=torch.float32, device=dev)
         ops.linear_scan(proj, 0, 1, proj, hd, 1, proj, 2 * hd, decay, 0, True, None, 0, None, float(D) ** -0.5, mem.state, ctx.seq_rows,
                         ctx.seq_slot, o, ctx.seqs, H, D, P, write_state=mem.writes)
         y = torch.empty((rows, hp), dtype=x.dtype, device=dev)
-        ops.gated_norm(o, proj, 2 * hd + hp, self.norm_weight, y, H, self.norm_eps, gate_first=False, factor=self.out_scale)
+        ops.gated_norm(o, proj, 2 * hd + hp, self.norm_weight, y, H, self.norm_eps, gate_first=False, factor=self.out_scale, row_slot=ctx.row_slot)
         products.linear(y, self.w_o, residual, products.EPI_ADD_F32, "output product")
 
 
@@ -137,14 +131,14 @@ class StateSpaceDual(Mixer):
         inner, C, dev = self.inner, self.channels, x.device
         proj = torch.empty((rows, self.w_in.shape[0]), dtype=torch.float32, device=dev)
         products.linear(x, self.w_in, proj, products.EPI_STORE_F32, "recurrence projections")
-        padded = ctx.decode or not ctx.host_seq_rows or ctx.host_seq_rows[-1] != rows
-        xbc = (torch.zeros if padded else torch.empty)((rows, C), dtype=torch.float32, device=dev)
-        dtda = (torch.zeros if padded else torch.empty)((rows, 2 * H), dtype=torch.float32, device=dev)
+        # Set-up and recurrence walk sequences: rows of no sequence are neither written nor read, and the norm at the end skips them.
+        xbc = torch.empty((rows, C), dtype=torch.float32, device=dev)
+        dtda = torch.empty((rows, 2 * H), dtype=torch.float32, device=dev)
         ops.ssd_prepare(proj, inner, inner + C, self.conv_t, self.conv_b, self.dt_bias, self.a_log, tail, ctx.seq_rows, ctx.seq_slot, xbc, dtda,
                         ctx.seqs, ctx.max_new, write_tail=mem.writes)
-        o = _scan_output(rows, inner, ctx, dev)
+        o = torch.empty((rows, inner), dtype=torch.float32, device=dev)
         ops.linear_scan(xbc, inner + G * N, H // G, xbc, inner, H // G, xbc, 0, dtda, H, False, dtda, 0, self.skip, 1.0, mem.state, ctx.seq_rows,
                         ctx.seq_slot, o, ctx.seqs, H, N, P, write_state=mem.writes)
         y = torch.empty((rows, inner), dtype=x.dtype, device=dev)
-        ops.gated_norm(o, proj, 0, self.norm_weight, y, self.norm_groups, self.norm_eps, gate_first=True, factor=self.out_scale)
+        ops.gated_norm(o, proj, 0, self.norm_weight, y, self.norm_groups, self.norm_eps, gate_first=True, factor=self.out_scale, row_slot=ctx.row_slot)
         products.linear(y, self.w_o, residual, products.EPI_ADD_F32, "output product")
